@@ -1,0 +1,313 @@
+// Planner: maps a bound kernel group onto the kernel families of the C ABI.
+// Matching is structural (index roles and tensor layouts), never by variable name.
+#include "Plan.hpp"
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <sstream>
+
+namespace acro
+{
+namespace plan
+{
+
+namespace
+{
+
+typedef std::vector<std::string> Names;
+
+Names indices_of(DimensionedKernel &k, int vari) { return vari < 0 ? k.OutputVar.IndexNames : k.InputVars[vari].IndexNames; }
+
+bool distinct(const Names &n)
+{
+    Names s = n;
+    std::sort(s.begin(), s.end());
+    return std::adjacent_find(s.begin(), s.end()) == s.end();
+}
+
+Names concat(const Names &a, const Names &b)
+{
+    Names r = a;
+    r.insert(r.end(), b.begin(), b.end());
+    return r;
+}
+
+bool is_subsequence(const Names &small, const Names &big)
+{
+    std::size_t j = 0;
+    for (std::size_t i = 0; i < big.size() && j < small.size(); ++i)
+    {
+        if (big[i] == small[j]) ++j;
+    }
+    return j == small.size();
+}
+
+int op_code(DimensionedKernel &k) { return k.EqOperator == "=" ? ACRO_B200_OP_ASSIGN : k.EqOperator == "+=" ? ACRO_B200_OP_ADD : ACRO_B200_OP_SUB; }
+
+std::int64_t extent_of(DimensionedKernel &k, const std::string &idx)
+{
+    std::string name = idx;
+    return k.GetLoopDim(name);
+}
+
+std::int64_t io_bytes(DimensionedKernel &k)
+{
+    std::int64_t entries = k.GetVarSize64(-1) * (k.EqOperator == "=" ? 1 : 2);
+    for (int vari = 0; vari < k.GetNumInputVars(); ++vari)
+    {
+        bool seen = false;   // the same tensor passed twice is read once
+        for (int prev = 0; prev < vari; ++prev) seen = seen || k.GetVarName(prev) == k.GetVarName(vari);
+        if (!seen) entries += k.GetVarSize64(vari);
+    }
+    return entries * 8;
+}
+
+// ---------------------------------------------------------------- generic
+Step plan_generic(DimensionedKernel &k, int ki)
+{
+    Step s;
+    s.family = Family::Generic;
+    s.kernels = {ki};
+    s.out.ki = ki;
+    s.op = op_code(k);
+    ACROBATIC_ASSERT(k.GetNumInputVars() <= ACRO_B200_MAX_INPUTS, "Too many input tensors in kernel:  " + k.KernelStr);
+
+    // Outer loops in the output's own dimension order (fastest last), then the
+    // contracted loops in summation order.
+    Names loops;
+    for (const std::string &idx : k.OutputVar.IndexNames)
+    {
+        if (std::find(loops.begin(), loops.end(), idx) == loops.end()) loops.push_back(idx);
+    }
+    const int n_outer = static_cast<int>(loops.size());
+    for (const std::string &idx : k.ContractionIndexNames) loops.push_back(idx);
+    ACROBATIC_ASSERT(loops.size() <= ACRO_B200_MAX_LOOPS, "Too many indices in kernel:  " + k.KernelStr);
+
+    acro_b200_generic_desc &g = s.generic;
+    std::memset(&g, 0, sizeof g);
+    g.n_loops = static_cast<int>(loops.size());
+    g.n_outer = n_outer;
+    g.n_inputs = k.GetNumInputVars();
+    g.op = s.op;
+    std::int64_t outer_points = 1, terms = 1;
+    for (int l = 0; l < g.n_loops; ++l)
+    {
+        g.extent[l] = extent_of(k, loops[l]);
+        (l < n_outer ? outer_points : terms) *= g.extent[l];
+    }
+    for (int vari = -1; vari < k.GetNumInputVars(); ++vari)
+    {
+        std::int64_t *step = vari < 0 ? g.out_step : g.in_step[vari];
+        Names idx = indices_of(k, vari);
+        for (int d = 0; d < static_cast<int>(idx.size()); ++d)
+        {
+            int l = static_cast<int>(std::find(loops.begin(), loops.end(), idx[d]) - loops.begin());
+            step[l] += k.GetVarDimStride64(vari, d);
+        }
+        if (vari >= 0)
+        {
+            TensorRef r;
+            r.ki = ki;
+            r.vari = vari;
+            s.ins.push_back(r);
+        }
+    }
+    s.zero_fill_first = (s.op == ACRO_B200_OP_ASSIGN) && outer_points < k.GetVarSize64(-1);
+    s.bytes = io_bytes(k);
+    s.flops = outer_points * terms * k.GetNumInputVars();   // (n_in - 1) multiplies + 1 add per term
+    std::ostringstream note;
+    note << "thread per output entry: " << outer_points << " entries x " << terms << " terms";
+    s.note = note.str();
+    return s;
+}
+
+// ---------------------------------------------------------------- reduce_batch
+// out_F = sum_n A_n_F [w_n]: one contracted index n that is the leading dimension of a
+// "row" operand whose remaining dimensions are exactly the output's.
+bool plan_reduce_batch(DimensionedKernel &k, int ki, Step &s)
+{
+    if (k.ContractionIndexNames.size() != 1 || !distinct(k.OutputVar.IndexNames)) return false;
+    if (k.GetNumInputVars() < 1 || k.GetNumInputVars() > 2) return false;
+    const std::string n = k.ContractionIndexNames[0];
+    const Names row_shape = concat(Names(1, n), k.OutputVar.IndexNames);
+    int row_var = -1, weight_var = -1;
+    for (int vari = 0; vari < k.GetNumInputVars(); ++vari)
+    {
+        Names idx = indices_of(k, vari);
+        if (idx == row_shape && row_var < 0) row_var = vari;
+        else if (idx == Names(1, n) && weight_var < 0) weight_var = vari;
+        else return false;
+    }
+    if (row_var < 0) return false;
+    const std::int64_t rows = extent_of(k, n);
+    const std::int64_t F = k.GetVarSize64(-1);
+    if (F > 1024 || !acro_b200_reduce_batch_supported(rows, static_cast<int>(F))) return false;
+
+    s = Step();
+    s.family = Family::ReduceBatch;
+    s.kernels = {ki};
+    s.out.ki = ki;
+    s.op = op_code(k);
+    s.rows = rows;
+    s.sizes[0] = static_cast<int>(F);
+    TensorRef a;
+    a.ki = ki;
+    a.vari = row_var;
+    s.ins.push_back(a);
+    if (weight_var >= 0)
+    {
+        TensorRef w;
+        w.ki = ki;
+        w.vari = weight_var;
+        s.ins.push_back(w);
+    }
+    s.bytes = rows * 8 * (F + (weight_var >= 0 ? 1 : 0)) + F * 8;
+    s.flops = rows * F * (weight_var >= 0 ? 2 : 1);
+    std::ostringstream note;
+    note << "streaming reduction over " << rows << " rows of " << F << " entries"
+         << (weight_var >= 0 ? ", weighted" : "") << "; fixed-order two-level combine";
+    s.note = note.str();
+    return true;
+}
+
+// ---------------------------------------------------------------- pointwise_sym
+// D_P_m_n = (scalars over P, left to right) X_P_m_l Y_P_n_l, the scalars first in the string.
+bool plan_pointwise_sym(DimensionedKernel &k, int ki, Step &s)
+{
+    const Names out = k.OutputVar.IndexNames;
+    if (k.ContractionIndexNames.size() != 1 || out.size() < 3 || !distinct(out)) return false;
+    const int nin = k.GetNumInputVars();
+    if (nin < 2 || nin - 2 > ACRO_B200_MAX_SCALARS) return false;
+    const std::string l = k.ContractionIndexNames[0];
+    const std::string m = out[out.size() - 2], n = out[out.size() - 1];
+    const Names P(out.begin(), out.end() - 2);
+    if (P.size() > ACRO_B200_MAX_POINT_LOOPS) return false;
+    const std::int64_t dim = extent_of(k, m);
+    if (extent_of(k, n) != dim || extent_of(k, l) != dim) return false;
+
+    Names xs = P, ys = P;
+    xs.push_back(m); xs.push_back(l);
+    ys.push_back(n); ys.push_back(l);
+    if (indices_of(k, nin - 2) != xs || indices_of(k, nin - 1) != ys) return false;
+
+    s = Step();
+    acro_b200_pointwise_desc &d = s.pointwise;
+    std::memset(&d, 0, sizeof d);
+    d.dim = static_cast<int>(dim);
+    d.op = op_code(k);
+    d.n_point_loops = static_cast<int>(P.size());
+    d.n_scalars = nin - 2;
+    std::int64_t points = 1;
+    for (std::size_t j = 0; j < P.size(); ++j)
+    {
+        d.point_extent[j] = extent_of(k, P[j]);
+        points *= d.point_extent[j];
+    }
+    std::int64_t scalar_entries = 0;
+    for (int vari = 0; vari < nin - 2; ++vari)
+    {
+        Names idx = indices_of(k, vari);
+        if (!distinct(idx) || !is_subsequence(idx, P)) return false;
+        for (int dd = 0; dd < static_cast<int>(idx.size()); ++dd)
+        {
+            int j = static_cast<int>(std::find(P.begin(), P.end(), idx[dd]) - P.begin());
+            d.scalar_step[vari][j] = k.GetVarDimStride64(vari, dd);
+        }
+        scalar_entries += k.GetVarSize64(vari);
+        TensorRef r;
+        r.ki = ki;
+        r.vari = vari;
+        s.ins.push_back(r);
+    }
+    if (!acro_b200_pointwise_sym_supported(&d)) return false;
+    TensorRef x, y;
+    x.ki = y.ki = ki;
+    x.vari = nin - 2;
+    y.vari = nin - 1;
+    s.ins.push_back(x);
+    s.ins.push_back(y);
+    s.family = Family::PointwiseSym;
+    s.kernels = {ki};
+    s.out.ki = ki;
+    s.op = d.op;
+    s.rows = points;
+    const bool same_xy = k.GetVarName(nin - 2) == k.GetVarName(nin - 1);
+    s.bytes = 8 * (points * dim * dim * ((same_xy ? 1 : 2) + (s.op == ACRO_B200_OP_ASSIGN ? 1 : 2)) + scalar_entries);
+    s.flops = points * dim * dim * dim * (nin);   // (nin-1) multiplies + 1 add per term
+    std::ostringstream note;
+    note << points << " points, " << dim << "x" << dim << " block per point, " << d.n_scalars
+         << " point-wise factors; tiles staged through shared memory";
+    s.note = note.str();
+    return true;
+}
+
+Step plan_single(DimensionedKernel &k, int ki)
+{
+    Step s;
+    if (plan_reduce_batch(k, ki, s)) return s;
+    if (plan_pointwise_sym(k, ki, s)) return s;
+    return plan_generic(k, ki);
+}
+
+}  // namespace
+
+const char *FamilyName(Family f)
+{
+    switch (f)
+    {
+        case Family::Generic: return "generic";
+        case Family::ReduceBatch: return "reduce_batch";
+        case Family::PointwiseSym: return "pointwise_sym";
+        case Family::Rank1Gemm: return "rank1_gemm";
+        case Family::BatchedGemm: return "batched_gemm";
+        case Family::SumfactMass: return "sumfact_mass";
+    }
+    return "?";
+}
+
+Program BuildProgram(DimensionedMultiKernel &mk, bool allow_elision)
+{
+    (void)allow_elision;
+    Program p;
+    for (int ki = 0; ki < mk.GetNumKernels(); ++ki)
+    {
+        p.steps.push_back(plan_single(*mk.Kernels[ki], ki));
+    }
+    for (const Step &s : p.steps)
+    {
+        if (s.family == Family::ReduceBatch)
+        {
+            p.scratch_bytes = std::max(p.scratch_bytes, acro_b200_reduce_batch_scratch_bytes(s.sizes[0]));
+        }
+    }
+    return p;
+}
+
+std::string Program::Describe(DimensionedMultiKernel &mk) const
+{
+    std::ostringstream os;
+    os << "acrotensor-b200 plan (sm_100a, ahead-of-time kernels)\n";
+    os << "kernels:";
+    for (DimensionedKernel *k : mk.Kernels) os << " [" << k->KernelStr << "]";
+    os << "\nloop order:";
+    for (int l = 0; l < mk.GetNumIndices(); ++l)
+    {
+        os << " " << mk.GetLoopIndex(l) << "(" << mk.GetLoopDim(l) << ")" << (mk.IsContractionLoop(l) ? "*" : "")
+           << (mk.IsSharedOuterLoop(l) ? "^" : "");
+    }
+    os << "   (* contracted, ^ shared outer)\n";
+    os << "unique variables: " << mk.GetNumUVars() << "\n";
+    for (std::size_t i = 0; i < steps.size(); ++i)
+    {
+        const Step &s = steps[i];
+        os << "step " << i << ": family=" << FamilyName(s.family) << " kernels=";
+        for (std::size_t j = 0; j < s.kernels.size(); ++j) os << (j ? "," : "") << s.kernels[j];
+        os << " bytes=" << s.bytes << " flops=" << s.flops << " | " << s.note << "\n";
+    }
+    if (scratch_bytes) os << "scratch: " << scratch_bytes << " bytes\n";
+    return os.str();
+}
+
+}
+}

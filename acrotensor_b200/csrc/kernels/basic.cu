@@ -1,0 +1,108 @@
+// Status plumbing, device discovery, fill and scale.
+#include "common.cuh"
+
+#include <mutex>
+#include <vector>
+
+namespace acro_b200_detail
+{
+
+static thread_local std::string g_last_error;
+
+void set_last_error(const std::string &text) { g_last_error = text; }
+
+int fail_invalid(const std::string &text)
+{
+    set_last_error(text);
+    return ACRO_B200_EINVAL;
+}
+
+int fail_unsupported(const std::string &text)
+{
+    set_last_error(text);
+    return ACRO_B200_EUNSUPPORTED;
+}
+
+int fail_cuda(cudaError_t status, const char *where)
+{
+    set_last_error(std::string("CUDA error in ") + where + ": " + cudaGetErrorString(status));
+    return ACRO_B200_ECUDA;
+}
+
+int sm_count()
+{
+    static std::mutex lock;
+    static std::vector<int> cache;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    std::lock_guard<std::mutex> guard(lock);
+    if (static_cast<int>(cache.size()) <= dev) cache.resize(dev + 1, 0);
+    if (cache[dev] == 0)
+    {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 0;
+        cache[dev] = n;
+    }
+    return cache[dev];
+}
+
+}
+
+using namespace acro_b200_detail;
+
+namespace
+{
+
+__global__ void fill_kernel(double *__restrict__ data, int64_t n, double val)
+{
+    int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) data[i] = val;
+}
+
+__global__ void scale_kernel(double *__restrict__ data, int64_t n, double c)
+{
+    int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) data[i] *= c;
+}
+
+int elementwise_grid(int64_t n)
+{
+    int64_t blocks = (n + 255) / 256;
+    int64_t cap = static_cast<int64_t>(sm_count() > 0 ? sm_count() : 1) * 16;
+    return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+}
+
+extern "C" {
+
+const char *acro_b200_last_error(void) { return g_last_error.c_str(); }
+
+int acro_b200_device_count(void)
+{
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess)
+    {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int acro_b200_fill(double *data, int64_t n, double val, void *stream)
+{
+    if (n < 0 || (n > 0 && data == nullptr)) return fail_invalid("acro_b200_fill: bad arguments");
+    if (n == 0) return ACRO_B200_OK;
+    fill_kernel<<<elementwise_grid(n), 256, 0, as_stream(stream)>>>(data, n, val);
+    return launch_status("acro_b200_fill");
+}
+
+int acro_b200_scale(double *data, int64_t n, double c, void *stream)
+{
+    if (n < 0 || (n > 0 && data == nullptr)) return fail_invalid("acro_b200_scale: bad arguments");
+    if (n == 0) return ACRO_B200_OK;
+    scale_kernel<<<elementwise_grid(n), 256, 0, as_stream(stream)>>>(data, n, c);
+    return launch_status("acro_b200_scale");
+}
+
+}

@@ -1,0 +1,36 @@
+// Shared plumbing of the kernel layer: status reporting and launch checks.
+#ifndef ACRO_B200_KERNELS_COMMON_CUH
+#define ACRO_B200_KERNELS_COMMON_CUH
+
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <string>
+
+#include "acro_b200.h"
+
+namespace acro_b200_detail
+{
+
+void set_last_error(const std::string &text);
+
+int fail_invalid(const std::string &text);
+int fail_unsupported(const std::string &text);
+int fail_cuda(cudaError_t status, const char *where);
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
+
+// To be called right after a kernel launch.
+inline int launch_status(const char *where)
+{
+    cudaError_t status = cudaGetLastError();
+    return status == cudaSuccess ? ACRO_B200_OK : fail_cuda(status, where);
+}
+
+__host__ __device__ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}
+
+#endif

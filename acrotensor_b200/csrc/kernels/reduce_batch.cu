@@ -1,0 +1,219 @@
+// reduce_batch: out[f] (op)= sum_n A[n*F + f] * w[n].
+//
+// A is read once as a flat stream of double2 words.  A tile is 2*T doubles, with the
+// thread count T a multiple of F, so a thread's two lanes keep fixed columns (f) for
+// the whole kernel and only the row advances.  Per-thread partial sums are combined
+// per column in a fixed order inside the CTA, then across CTAs by whichever CTA
+// finishes last (ticket counter), again in a fixed order: results do not depend on
+// scheduling.
+//
+// Algorithmic HBM traffic: 8*F bytes of A and 8 bytes of w per row.
+#include "common.cuh"
+
+using namespace acro_b200_detail;
+
+namespace
+{
+
+constexpr int kMaxThreads = 512;
+constexpr int kMaxGrid = 2048;
+constexpr int kUnroll = 4;
+constexpr size_t kCounterBytes = 256;   // keeps the partial sums 256-byte aligned
+
+__host__ __device__ inline int threads_for(int F) { return (kMaxThreads / F) * F; }
+
+struct ReduceArgs
+{
+    const double *A;
+    const double *w;
+    double *out;
+    int64_t rows;
+    int F;
+    int op;
+    unsigned int *counter;
+    double *partials;   // [gridDim.x][F]
+};
+
+template <bool WEIGHTED, bool VECTOR>
+__global__ void __launch_bounds__(kMaxThreads)
+reduce_batch_kernel(const ReduceArgs a)
+{
+    extern __shared__ double lanes[];   // 2*T per-lane sums, reused by the final combine
+    __shared__ bool is_last;
+
+    const int F = a.F;
+    const int T = blockDim.x;
+    const int t = threadIdx.x;
+    const int64_t tile_doubles = 2 * static_cast<int64_t>(T);
+    const int64_t tile_rows = tile_doubles / F;
+    const int64_t full_tiles = a.rows / tile_rows;
+
+    // Columns and row offsets of this thread's two lanes inside a tile.
+    const int e0 = 2 * t, e1 = 2 * t + 1;
+    const int r0 = e0 / F, r1 = e1 / F;
+    double acc0 = 0.0, acc1 = 0.0;
+
+    int64_t tile = blockIdx.x;
+    // Main loop: kUnroll independent tiles in flight per thread.
+    for (; tile + static_cast<int64_t>(kUnroll - 1) * gridDim.x < full_tiles; tile += static_cast<int64_t>(kUnroll) * gridDim.x)
+    {
+        double2 v[kUnroll];
+        double w0[kUnroll], w1[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+        {
+            const int64_t tl = tile + static_cast<int64_t>(u) * gridDim.x;
+            const double *src = a.A + tl * tile_doubles + e0;
+            if (VECTOR) v[u] = __ldcs(reinterpret_cast<const double2 *>(src));
+            else { v[u].x = __ldcs(src); v[u].y = __ldcs(src + 1); }
+            if (WEIGHTED)
+            {
+                const int64_t row = tl * tile_rows;
+                w0[u] = __ldg(a.w + row + r0);
+                w1[u] = __ldg(a.w + row + r1);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+        {
+            if (WEIGHTED) { acc0 = fma(v[u].x, w0[u], acc0); acc1 = fma(v[u].y, w1[u], acc1); }
+            else { acc0 += v[u].x; acc1 += v[u].y; }
+        }
+    }
+    for (; tile < full_tiles; tile += gridDim.x)
+    {
+        const double *src = a.A + tile * tile_doubles + e0;
+        double2 v;
+        if (VECTOR) v = __ldcs(reinterpret_cast<const double2 *>(src));
+        else { v.x = __ldcs(src); v.y = __ldcs(src + 1); }
+        if (WEIGHTED)
+        {
+            const int64_t row = tile * tile_rows;
+            acc0 = fma(v.x, __ldg(a.w + row + r0), acc0);
+            acc1 = fma(v.y, __ldg(a.w + row + r1), acc1);
+        }
+        else { acc0 += v.x; acc1 += v.y; }
+    }
+    // Ragged tail (fewer rows than a tile): handled by the CTA whose turn it would be.
+    if (static_cast<int64_t>(blockIdx.x) == full_tiles % gridDim.x)
+    {
+        const int64_t row_base = full_tiles * tile_rows;
+        const int64_t left = a.rows - row_base;
+        if (r0 < left)
+        {
+            const double x = a.A[(row_base + r0) * F + (e0 - r0 * F)];
+            acc0 = WEIGHTED ? fma(x, a.w[row_base + r0], acc0) : acc0 + x;
+        }
+        if (r1 < left)
+        {
+            const double x = a.A[(row_base + r1) * F + (e1 - r1 * F)];
+            acc1 = WEIGHTED ? fma(x, a.w[row_base + r1], acc1) : acc1 + x;
+        }
+    }
+
+    // CTA combine: lane e belongs to column e % F; column sums in ascending lane order.
+    lanes[e0] = acc0;
+    lanes[e1] = acc1;
+    __syncthreads();
+    if (t < F)
+    {
+        double s = 0.0;
+        for (int e = t; e < 2 * T; e += F) s += lanes[e];
+        a.partials[static_cast<int64_t>(blockIdx.x) * F + t] = s;
+    }
+
+    // Ticket: the CTA that arrives last combines all partial sums.
+    __threadfence();
+    __syncthreads();
+    if (t == 0)
+    {
+        const unsigned int ticket = atomicAdd(a.counter, 1u);
+        is_last = (ticket == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+
+    // Thread (column c = t % F, slot j = t / F) adds partials of CTAs j, j+J, ...; then
+    // column c adds its J slot sums in ascending order.
+    const int J = T / F;
+    const int c = t % F, j = t / F;
+    double s = 0.0;
+    for (int g = j; g < static_cast<int>(gridDim.x); g += J) s += __ldcg(a.partials + static_cast<int64_t>(g) * F + c);
+    lanes[j * F + c] = s;
+    __syncthreads();
+    if (t < F)
+    {
+        double total = 0.0;
+        for (int jj = 0; jj < J; ++jj) total += lanes[jj * F + t];
+        if (a.op == ACRO_B200_OP_ASSIGN) a.out[t] = total;
+        else if (a.op == ACRO_B200_OP_ADD) a.out[t] += total;
+        else a.out[t] -= total;
+    }
+    if (t == 0) *a.counter = 0u;   // leave the scratch ready for the next call
+}
+
+}
+
+extern "C" {
+
+size_t acro_b200_reduce_batch_scratch_bytes(int F)
+{
+    if (F < 1) return 0;
+    return kCounterBytes + static_cast<size_t>(kMaxGrid) * static_cast<size_t>(F) * sizeof(double);
+}
+
+int acro_b200_reduce_batch_supported(int64_t rows, int F)
+{
+    return (F >= 1 && F <= kMaxThreads / 2 && rows >= 256) ? 1 : 0;
+}
+
+int acro_b200_reduce_batch(const double *A, const double *w, double *out, int64_t rows, int F, int op,
+                           double *scratch, size_t scratch_bytes, void *stream)
+{
+    if (A == nullptr || out == nullptr || scratch == nullptr) return fail_invalid("acro_b200_reduce_batch: null argument");
+    if (rows < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_reduce_batch: bad rows or operator");
+    if (F < 1 || F > kMaxThreads / 2) return fail_unsupported("acro_b200_reduce_batch: row length must be 1..256");
+    if (scratch_bytes < acro_b200_reduce_batch_scratch_bytes(F)) return fail_invalid("acro_b200_reduce_batch: scratch buffer too small");
+    if ((reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) return fail_invalid("acro_b200_reduce_batch: scratch must be 256-byte aligned");
+    const int sms = sm_count();
+    if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_reduce_batch");
+
+    const int T = threads_for(F);
+    const int64_t tile_rows = 2 * static_cast<int64_t>(T) / F;
+    const int64_t tiles = (rows + tile_rows - 1) / tile_rows;
+    int64_t grid = static_cast<int64_t>(sms) * (2048 / T > 0 ? 2048 / T : 1);
+    if (grid > tiles) grid = tiles;
+    if (grid > kMaxGrid) grid = kMaxGrid;
+    if (grid < 1) grid = 1;
+
+    ReduceArgs args;
+    args.A = A;
+    args.w = w;
+    args.out = out;
+    args.rows = rows;
+    args.F = F;
+    args.op = op;
+    args.counter = reinterpret_cast<unsigned int *>(scratch);
+    args.partials = reinterpret_cast<double *>(reinterpret_cast<char *>(scratch) + kCounterBytes);
+
+    cudaStream_t s = as_stream(stream);
+    cudaError_t status = cudaMemsetAsync(args.counter, 0, kCounterBytes, s);
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_reduce_batch (counter reset)");
+    const size_t smem = 2 * static_cast<size_t>(T) * sizeof(double);
+    const bool vec = aligned16(A);
+    const int g = static_cast<int>(grid);
+    if (w != nullptr)
+    {
+        if (vec) reduce_batch_kernel<true, true><<<g, T, smem, s>>>(args);
+        else reduce_batch_kernel<true, false><<<g, T, smem, s>>>(args);
+    }
+    else
+    {
+        if (vec) reduce_batch_kernel<false, true><<<g, T, smem, s>>>(args);
+        else reduce_batch_kernel<false, false><<<g, T, smem, s>>>(args);
+    }
+    return launch_status("acro_b200_reduce_batch");
+}
+
+}

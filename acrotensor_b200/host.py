@@ -1,0 +1,224 @@
+"""Python mirror of acro::Tensor / acro::SliceTensor / acro::TensorEngine over the C ABI.
+
+Method names and argument meaning follow the reference's C++ API
+(tensor/Tensor.hpp:15-127, tensor/SliceTensor.hpp:14-57,
+kernel/TensorEngine.hpp:26-86 of LLNL/acrotensor); failures raise AcroError
+where the C++ API throws std::runtime_error.
+"""
+import ctypes
+
+import numpy as np
+
+from . import _lib
+from ._lib import check, lib
+
+
+def device_count():
+    return lib().acro_b200_device_count()
+
+
+def isCudaReady():
+    return device_count() > 0
+
+
+def set_stream(stream_ptr):
+    """Library-wide CUDA stream (an integer cudaStream_t; 0 = legacy default stream)."""
+    check(lib().acro_b200_set_stream(ctypes.c_void_p(stream_ptr or 0)))
+
+
+def _text(fn, *args, size=1 << 16):
+    buf = ctypes.create_string_buffer(size)
+    check(fn(*args, buf, size))
+    return buf.value.decode()
+
+
+def describe_kernel(kernel):
+    """Parser view of a contraction string (no device needed)."""
+    return _text(lib().acro_b200_describe_kernel, kernel.encode())
+
+
+def describe_plan(kernels, shapes, transient_intermediates=False):
+    """Planner view of a kernel group bound to shapes (no device, no data needed).
+    ``shapes[k]`` lists the output shape and then each input shape of kernel k."""
+    n = len(kernels)
+    ks = (ctypes.c_char_p * n)(*[k.encode() for k in kernels])
+    flat = [d for per_kernel in shapes for shape in per_kernel for d in shape]
+    dims = (ctypes.c_int * len(flat))(*flat)
+    buf = ctypes.create_string_buffer(1 << 16)
+    check(lib().acro_b200_describe_plan(n, ks, dims, int(transient_intermediates), buf, len(buf)))
+    return buf.value.decode()
+
+
+class Tensor:
+    """acro::Tensor.  ``Tensor(d0, d1, ...)`` owns its host buffer; ``Tensor(shape, hdata=ndarray)``
+    views a float64 C-contiguous numpy array; ``ddata`` is an integer device pointer (or an object
+    with ``data_ptr()``, e.g. a torch CUDA tensor) used as the externally owned device mirror."""
+
+    def __init__(self, *dims, hdata=None, ddata=None, ongpu=False, _handle=None, _keep=None):
+        self._keep = [_keep, hdata, ddata]
+        if _handle is not None:
+            self._h = _handle
+            return
+        if len(dims) == 1 and isinstance(dims[0], (list, tuple)):
+            dims = tuple(dims[0])
+        if hdata is not None:
+            if not (isinstance(hdata, np.ndarray) and hdata.dtype == np.float64 and hdata.flags.c_contiguous):
+                raise TypeError("hdata must be a C-contiguous float64 numpy array")
+            if not dims:
+                dims = hdata.shape
+        hptr = hdata.ctypes.data if hdata is not None else None
+        dptr = ddata.data_ptr() if hasattr(ddata, "data_ptr") else ddata
+        arr = (ctypes.c_int * len(dims))(*[int(d) for d in dims])
+        h = ctypes.c_void_p()
+        check(lib().acro_tensor_create(len(dims), arr, hptr, dptr, int(bool(ongpu)), ctypes.byref(h)))
+        self._h = h
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h is not None and _lib._lib is not None:
+            _lib._lib.acro_tensor_destroy(h)
+
+    # shape ---------------------------------------------------------------
+    def GetRank(self):
+        return lib().acro_tensor_rank(self._h)
+
+    def GetSize(self):
+        return lib().acro_tensor_size(self._h)
+
+    def GetDim(self, d):
+        r = lib().acro_tensor_dim(self._h, d)
+        if r < 0:
+            raise IndexError("dimension out of range")
+        return r
+
+    @property
+    def shape(self):
+        return tuple(self.GetDim(d) for d in range(self.GetRank()))
+
+    def Reshape(self, *dims):
+        if len(dims) == 1 and isinstance(dims[0], (list, tuple)):
+            dims = tuple(dims[0])
+        arr = (ctypes.c_int * len(dims))(*dims)
+        check(lib().acro_tensor_reshape(self._h, len(dims), arr))
+
+    # data ----------------------------------------------------------------
+    def GetData(self):
+        return lib().acro_tensor_data(self._h)
+
+    def GetDeviceData(self):
+        return lib().acro_tensor_device_data(self._h)
+
+    def GetCurrentData(self):
+        return self.GetDeviceData() if self.IsOnGPU() else self.GetData()
+
+    def numpy(self):
+        """The host buffer as a numpy view (valid while this Tensor lives)."""
+        n = self.GetSize()
+        buf = (ctypes.c_double * n).from_address(self.GetData())
+        return np.frombuffer(buf, dtype=np.float64).reshape(self.shape)
+
+    def Retarget(self, hdata, ddata=None):
+        self._keep += [hdata, ddata]
+        dptr = ddata.data_ptr() if hasattr(ddata, "data_ptr") else ddata
+        check(lib().acro_tensor_retarget(self._h, hdata.ctypes.data, dptr))
+
+    # GPU motion ------------------------------------------------------------
+    def MapToGPU(self):
+        check(lib().acro_tensor_map_to_gpu(self._h))
+
+    def MoveToGPU(self):
+        check(lib().acro_tensor_move_to_gpu(self._h))
+
+    def SwitchToGPU(self):
+        check(lib().acro_tensor_switch_to_gpu(self._h))
+
+    def UnmapFromGPU(self):
+        check(lib().acro_tensor_unmap_from_gpu(self._h))
+
+    def MoveFromGPU(self):
+        check(lib().acro_tensor_move_from_gpu(self._h))
+
+    def SwitchFromGPU(self):
+        check(lib().acro_tensor_switch_from_gpu(self._h))
+
+    def IsMappedToGPU(self):
+        return bool(lib().acro_tensor_is_mapped_to_gpu(self._h))
+
+    def IsOnGPU(self):
+        return bool(lib().acro_tensor_is_on_gpu(self._h))
+
+    def IsInitialized(self):
+        return True
+
+    def Set(self, val):
+        check(lib().acro_tensor_set(self._h, float(val)))
+
+    def Mult(self, c):
+        check(lib().acro_tensor_mult(self._h, float(c)))
+
+    def SetTransient(self, flag=True):
+        check(lib().acro_tensor_set_transient(self._h, int(bool(flag))))
+
+
+class SliceTensor(Tensor):
+    """acro::SliceTensor(T, i0, ...): the trailing dimensions of T at a fixed prefix."""
+
+    def __init__(self, parent, *indices):
+        arr = (ctypes.c_int * len(indices))(*indices)
+        h = ctypes.c_void_p()
+        check(lib().acro_tensor_slice(parent._h, len(indices), arr, ctypes.byref(h)))
+        super().__init__(_handle=h, _keep=parent)
+
+
+class TensorEngine:
+    """acro::TensorEngine.  ``TE("S_i_j = A_n_i_j B_n", S, A, B)`` runs one contraction;
+    Begin/EndMultiKernelLaunch record several and run them as one unit."""
+
+    def __init__(self, exec_type="Cuda"):
+        h = ctypes.c_void_p()
+        check(lib().acro_engine_create(exec_type.encode(), ctypes.byref(h)))
+        self._h = h
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h is not None and _lib._lib is not None:
+            _lib._lib.acro_engine_destroy(h)
+
+    def SetExecutorType(self, exec_type):
+        check(lib().acro_engine_set_executor_type(self._h, exec_type.encode()))
+
+    def GetExecType(self):
+        return _text(lib().acro_engine_exec_type, self._h, size=64)
+
+    @staticmethod
+    def _handles(inputs):
+        return (ctypes.c_void_p * len(inputs))(*[t._h for t in inputs])
+
+    def __call__(self, kernel, out, *inputs):
+        if len(inputs) == 1 and isinstance(inputs[0], (list, tuple)):
+            inputs = tuple(inputs[0])
+        check(lib().acro_engine_contract(self._h, kernel.encode(), out._h, len(inputs), self._handles(inputs)))
+
+    def GetImplementation(self, kernel, out, *inputs):
+        buf = ctypes.create_string_buffer(1 << 16)
+        check(lib().acro_engine_implementation(self._h, kernel.encode(), out._h, len(inputs),
+                                               self._handles(inputs), buf, len(buf)))
+        return buf.value.decode()
+
+    def BeginMultiKernelLaunch(self):
+        check(lib().acro_engine_begin_multi(self._h))
+
+    def EndMultiKernelLaunch(self):
+        check(lib().acro_engine_end_multi(self._h))
+
+    def EndMultiKernelLaunchDescribe(self):
+        return _text(lib().acro_engine_end_multi_describe, self._h)
+
+    def Clear(self):
+        check(lib().acro_engine_clear(self._h))
+
+    def IsGPUAvailable(self):
+        return isCudaReady()
+
+    def SetCudaStream(self, stream_ptr):
+        check(lib().acro_engine_set_stream(self._h, ctypes.c_void_p(stream_ptr or 0)))

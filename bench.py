@@ -1,0 +1,463 @@
+#!/usr/bin/env python
+"""Benchmark of the contraction hot path: string contraction -> dimension binding -> GPU kernel.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload suite|cfg0..cfg4]
+                    [--impl ours|reference] [--scaling weak|strong] [--scale F]
+
+A "step" is one pass of the selected workload(s) over one batch of seeded synthetic input.
+The default workload, "suite", runs the five benchmark configurations back to back; the
+headline `value` is the suite's algorithmic GB/s (sum of algorithmic bytes / step time) with
+inputs resident in HBM, and `per_config` carries GB/s, GFLOP/s and roofline fraction of every
+configuration.  `e2e` is the same metric through the public engine API with HOST buffers
+(pinned), host->device and device->host copies inside the timed region.
+
+For N > 1 launch with torchrun (one rank per GPU).  The batch index is cut into per-rank
+slabs; "weak" (default) gives every rank a full-size slab, "strong" splits the full size.
+Only the README reduction (batch index contracted) needs a collective: one all-reduce of
+its 3x3 result per step, inside the timed region.
+
+`--impl reference` times the reference's own CPU executor (the unmodified sources compiled
+into oracle/_ref, else the C restatement) on all host threads, on bounded samples.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+# fp64 peak of a B200 measured on this pool with a register-resident DFMA chain
+# (profiles/fp64_peak_microbenchmark.md); used for the compute-bound configurations.
+FP64_PEAK_GFLOPS_FILE = os.path.join(ROOT, "profiles", "fp64_peak_gflops.txt")
+# dram bytes (read+write) per launch of the dominant kernel from the ncu capture summarised
+# in profiles/ (scaled to a full-size launch); None until captured.
+NCU_TRAFFIC_BYTES = {}
+
+# batch of the bounded CPU sample per configuration (about 1-2 s of one core each)
+CPU_SAMPLE = {"cfg0": 1 << 24, "cfg1": 1 << 12, "cfg2": 1 << 16, "cfg3": 1 << 16, "cfg4": 1 << 9}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def fp64_peak_gflops():
+    try:
+        with open(FP64_PEAK_GFLOPS_FILE) as f:
+            return float(f.read().split()[0])
+    except Exception:
+        return 37000.0     # datasheet-level figure until the microbenchmark is recorded
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle sampling during the timed region (read-only queries)."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def selected(workload):
+    from acrotensor_b200.workloads import BY_KEY, WORKLOADS
+    return list(WORKLOADS) if workload == "suite" else [BY_KEY[workload]]
+
+
+def local_batch(w, args, rank, world):
+    from acrotensor_b200.runner import slab
+    full = max(1, int(round(w.batch * args.scale)))
+    if args.scaling == "weak" or world == 1:
+        return full
+    b0, b1 = slab(full, rank, world)
+    return b1 - b0
+
+
+# ----------------------------------------------------------------------------- our arm
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import acrotensor_b200 as ab
+    from acrotensor_b200.runner import Session, allreduce_partial
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit("--gpus %d does not match WORLD_SIZE %d" % (args.gpus, world))
+    if args.gpus > 1 and world == 1:
+        raise SystemExit("launch N>1 with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
+    if not os.path.exists(ab.LIB_PATH):
+        raise SystemExit("libacrotensor.so is missing and there is no fallback: run __graft_entry__.build()")
+    if not torch.cuda.is_available() or ab.device_count() == 0:
+        raise SystemExit("bench.py needs a CUDA device: the contraction path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    workloads = selected(args.workload)
+    sessions, outs_dev, batches = [], [], []
+    h2d = d2h = 0
+    for w in workloads:
+        b = local_batch(w, args, rank, world)
+        batches.append(b)
+        dev_t = w.make_inputs_device(b, dev, seed=args.seed, rank=rank)
+        host = {}
+        for name, shape in w.shapes(b).items():
+            if name in dev_t:
+                pinned = torch.empty(shape, dtype=torch.float64, pin_memory=True)
+                pinned.copy_(dev_t[name])
+                h2d += pinned.numel() * 8
+            elif w.tensors[name][2] == "out":
+                pinned = torch.empty(shape, dtype=torch.float64, pin_memory=True)
+                dev_t[name] = torch.zeros(shape, dtype=torch.float64, device=dev)
+                d2h += pinned.numel() * 8
+            else:
+                # chain intermediates: transient, elided by the fused plan; a one-entry
+                # placeholder would not bind, so they get real (never touched) storage
+                pinned = torch.empty(shape, dtype=torch.float64)
+                dev_t[name] = torch.empty(shape, dtype=torch.float64, device=dev)
+            host[name] = pinned.numpy()
+            dev_t[name + "/pinned"] = pinned
+        torch.cuda.synchronize()
+        sess = Session(w, host, device={n: t for n, t in dev_t.items() if "/" not in n}, transient=True)
+        sess.keep = dev_t
+        sessions.append(sess)
+        outs_dev.append({n: dev_t[n] for n in w.names("out")})
+
+    def make_resident():
+        for sess in sessions:
+            sess.to_device()
+            sess.mark_outputs_on_device()
+        torch.cuda.synchronize()
+
+    def device_step(events=None):
+        for i, (w, sess) in enumerate(zip(workloads, sessions)):
+            if events is not None:
+                events[i][0].record()
+            sess.run()
+            if w.batch_contracted and world > 1:
+                allreduce_partial(outs_dev[i][w.names("out")[0]])
+            if events is not None:
+                events[i][1].record()
+
+    make_resident()
+    plans = [sess.plan_text() for sess in sessions]
+    launches_per_step = sum(p.count("\nstep ") for p in plans)
+    for _ in range(args.warmup):
+        device_step()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in workloads]
+          for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for k in range(args.steps):
+        device_step(ev[k])
+    t1.record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = t0.elapsed_time(t1)
+    per_cfg_ms = [float(np.median([ev[k][i][0].elapsed_time(ev[k][i][1]) for k in range(args.steps)]))
+                  for i in range(len(workloads))]
+
+    # parity spot check of what was just computed (sampled units, untimed)
+    parity = spot_check(workloads, sessions, batches, world) if rank == 0 else None
+
+    # end to end: host buffers, copies inside the timed region
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+
+    def e2e_step():
+        for i, (w, sess) in enumerate(zip(workloads, sessions)):
+            for name in w.names("in"):
+                sess.t[name].SwitchFromGPU()          # the host copy is the fresh one again
+            for name in w.names("out") + w.names("tmp"):
+                sess.t[name].SwitchFromGPU()
+            sess.run()                                  # implicit MoveToGPU of every input (H2D)
+            if w.batch_contracted and world > 1:
+                allreduce_partial(outs_dev[i][w.names("out")[0]])
+            sess.fetch()                                # MoveFromGPU of the result (D2H)
+
+    e2e_step()
+    barrier()
+    w0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_ms = (time.perf_counter() - w0) * 1e3 / e2e_steps
+
+    times = torch.tensor([total_ms, e2e_ms] + per_cfg_ms, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    times = times.tolist()
+    total_ms, e2e_ms, per_cfg_ms = times[0], times[1], times[2:]
+
+    if rank == 0:
+        hbm_peak, peak_kind = measured_peaks()
+        fp64_peak = fp64_peak_gflops()
+        ms_per_step = total_ms / args.steps
+        glob = [b * world if (args.scaling == "weak" or world == 1) else max(1, int(round(w.batch * args.scale)))
+                for w, b in zip(workloads, batches)]
+        total_bytes = sum(w.bytes(g) for w, g in zip(workloads, glob))
+        total_flops = sum(w.flops(g) for w, g in zip(workloads, glob))
+        per_config = {}
+        for w, g, ms, b in zip(workloads, glob, per_cfg_ms, batches):
+            gbs = w.bytes(g) / ms * 1e-6
+            gfl = w.flops(g) / ms * 1e-6
+            per_config[w.key] = {
+                "batch": g, "ms": round(ms, 4), "GBps": round(gbs, 1), "GFLOPps": round(gfl, 1),
+                "bound": w.bound, "frac_hbm": round(gbs / (hbm_peak * world), 4),
+                "frac_fp64": round(gfl / (fp64_peak * world), 4)}
+        # the dominant kernel: the one with the largest share of the step
+        dom = int(np.argmax(per_cfg_ms))
+        wd = workloads[dom]
+        dom_bytes = wd.bytes(batches[dom])
+        if wd.bound == "hbm":
+            achieved = dom_bytes / per_cfg_ms[dom] * 1e-6
+            roof = {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
+                    "frac": round(achieved / hbm_peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(wd.key),
+                    "kernel": wd.key, "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback",
+                    "algorithmic_bytes_per_launch": dom_bytes}
+        else:
+            achieved = wd.flops(batches[dom]) / per_cfg_ms[dom] * 1e-9
+            roof = {"bound": "tensor", "achieved": round(achieved, 2), "peak": round(fp64_peak * 1e-3, 2), "unit": "TFLOP/s",
+                    "frac": round(achieved / (fp64_peak * 1e-3), 4), "traffic": NCU_TRAFFIC_BYTES.get(wd.key),
+                    "kernel": wd.key, "peak_source": "fp64 DFMA microbenchmark on this pool (not in MEASURED_PEAKS.json)",
+                    "algorithmic_flops_per_launch": wd.flops(batches[dom])}
+        line = {
+            "metric": "contraction_throughput", "value": round(total_bytes / ms_per_step * 1e-6, 1), "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f64",
+            "data": "synthetic (seeded, shapes and distributions of the benchmark configurations)",
+            "config": {"workload": args.workload + (": cfg0..cfg4 back to back" if args.workload == "suite" else ""),
+                       "batches_per_gpu": {w.key: b for w, b in zip(workloads, batches)},
+                       "l2": "inputs_exceed_l2 (every configuration streams >= 1.6 GB per GPU)" if args.scale >= 1 else "scaled-down run",
+                       "parallelism": "batch slabs x%d, all-reduce only for the contracted batch index" % world},
+            "gflops": round(total_flops / ms_per_step * 1e-6, 1),
+            "per_config": per_config,
+            "roofline": roof,
+            "e2e": {"value": round(total_bytes / e2e_ms * 1e-6, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 2), "steps": e2e_steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "parity": parity,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(workloads, args)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def spot_check(workloads, sessions, batches, world):
+    """Compares a few batch units of every result with the C restatement (untimed)."""
+    import torch
+    from oracle import oracle
+    worst = {}
+    for w, sess, b in zip(workloads, sessions, batches):
+        if w.batch_contracted:
+            if world > 1:
+                continue      # the all-reduced value mixes every rank's data
+            out = w.names("out")[0]
+            got = sess.keep[out].cpu().numpy()
+            # column sums recomputed on the device data with torch's fp64 tree reduction
+            a = sess.keep["A"]
+            ref = (a.view(b, -1).to(torch.float64) * sess.keep["B"].view(b, 1)).sum(dim=0).cpu().numpy().reshape(got.shape)
+            worst[w.key] = float(np.max(np.abs(got - ref) / np.abs(ref)))
+            continue
+        take = sorted(set([0, b // 2, b - 1]))
+        tensors = {}
+        for name in w.tensors:
+            t = sess.keep[name]
+            tensors[name] = (t[take].cpu().numpy() if w.batched(name) else t.cpu().numpy()).copy()
+        names = sorted(tensors)
+        got = {n: tensors[n].copy() for n in w.names("out")}
+        mags = [np.abs(tensors[n]) for n in names]
+        prog = [(k, names.index(o), [names.index(i) for i in ins]) for k, o, ins in w.program]
+        oracle.run("port", [tensors[n] for n in names], prog, multi=w.multi)
+        oracle.run("port", mags, prog, multi=w.multi)
+        worst[w.key] = max(oracle.parity_error(got[n], tensors[n], mags[names.index(n)]) for n in w.names("out"))
+    return {"max_err_over_sum_abs_terms": worst, "tolerance": 1e-12,
+            "note": "cfg0 vs a device-side fp64 tree sum (relative); others vs the oracle on sampled units"}
+
+
+# ----------------------------------------------------------------------------- CPU arms
+
+def cpu_time_workload(w, batch, threads, seed=0):
+    """Seconds the reference CPU executor needs for `batch` units of workload w."""
+    from oracle import oracle
+    from acrotensor_b200.runner import alloc_host
+    host = alloc_host(w, batch, w.make_inputs(batch, seed=seed))
+    names = sorted(host)
+    prog = [(k, names.index(o), [names.index(i) for i in ins]) for k, o, ins in w.program]
+    arrays = [host[n] for n in names]
+    t0 = time.perf_counter()
+    if oracle.have("ref"):
+        oracle.run_ref_slabs(arrays, prog, [w.batched(n) for n in names], batch, threads, multi=w.multi)
+        kind = "reference"
+    else:
+        oracle.run("port", arrays, prog, multi=w.multi)
+        kind = "port"
+    return time.perf_counter() - t0, kind
+
+
+def cpu_suite(workloads, args, threads, sample_scale):
+    """Runs a bounded sample of every workload and extrapolates to the full batch (the
+    interpreted executor's cost is linear in the batch)."""
+    full_seconds, detail, kind = 0.0, {}, "port"
+    for w in workloads:
+        sample = max(1, min(int(w.batch * args.scale), int(CPU_SAMPLE[w.key] * sample_scale)))
+        sec, kind = cpu_time_workload(w, sample, threads, seed=args.seed)
+        full = sec * (max(1, int(round(w.batch * args.scale))) / sample)
+        full_seconds += full
+        detail[w.key] = {"sample_batch": sample, "sample_s": round(sec, 3), "full_s_extrapolated": round(full, 2)}
+    total_bytes = sum(w.bytes(max(1, int(round(w.batch * args.scale)))) for w in workloads)
+    return total_bytes / full_seconds * 1e-9, full_seconds, detail, kind
+
+
+def host_threads():
+    from oracle import oracle
+    try:
+        return min(oracle.hardware_threads(), len(os.sched_getaffinity(0)))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def cpu_baseline(workloads, args):
+    from oracle import oracle
+    threads = host_threads() if oracle.have("ref") else 1
+    gbs, full_s, detail, kind = cpu_suite(workloads, args, threads, sample_scale=max(1.0, threads / 4.0))
+    return {"value": round(gbs, 4), "unit": "GB/s", "cores": threads, "kind": kind,
+            "sample": "per configuration a leading slab of the batch (sizes in detail), time scaled linearly to the full batch",
+            "full_suite_seconds_extrapolated": round(full_s, 1), "detail": detail}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+    if not oracle.have("port"):
+        oracle.build()
+    workloads = selected(args.workload)
+    threads = host_threads() if oracle.have("ref") else 1
+    sample_scale = max(1.0, threads / 4.0)
+    for _ in range(args.warmup):
+        cpu_suite(workloads, args, threads, sample_scale * 0.25)
+    vals, secs = [], []
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        gbs, full_s, detail, kind = cpu_suite(workloads, args, threads, sample_scale)
+        vals.append(gbs)
+        secs.append(full_s)
+    wall = time.perf_counter() - t0
+    value = float(np.median(vals))
+    base = {"value": round(value, 4), "unit": "GB/s", "cores": threads, "kind": kind,
+            "sample": "per configuration a leading slab of the batch, time scaled linearly to the full batch",
+            "detail": detail}
+    print(json.dumps({
+        "impl": "reference", "metric": "contraction_throughput", "value": round(value, 4), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(float(np.median(secs)) * 1e3, 1), "higher_is_better": True, "scaling": args.scaling,
+        "vs_baseline": None, "dtype": "f64", "data": "synthetic (seeded)",
+        "config": {"workload": args.workload + (": cfg0..cfg4 back to back" if args.workload == "suite" else ""),
+                   "note": "reference CPUInterpreted executor on the host cores; ms_per_step is the full-size suite extrapolated from the sample",
+                   "wall_s": round(wall, 1)},
+        "cpu_baseline": base,
+        "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="suite", choices=["suite", "cfg0", "cfg1", "cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scale", type=float, default=1.0, help="multiplies every batch size (debugging; 1.0 = benchmark sizes)")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,37 @@
+// Device/runtime helpers of the acro:: API that survive from util/CudaUtil.hpp
+// of LLNL/acrotensor: isCudaReady() (:175-184), setCudaContext() (:93-98) and
+// the error-check convention (:59-89).  The NVRTC machinery (CudaKernel) has
+// no counterpart here: kernels are compiled ahead of time for sm_100a.
+#ifndef ACRO_B200_CUDA_UTIL_HPP
+#define ACRO_B200_CUDA_UTIL_HPP
+
+#include <string>
+#include "Error.hpp"
+
+namespace acro
+{
+
+// True when a CUDA device can be used by this process.
+bool isCudaReady();
+
+// Adopt an externally created driver context (a CUcontext passed as void*)
+// for the calling thread; later library calls run in it.
+void setCudaContext(void *cuda_context);
+
+// The stream every kernel launch and copy of the library is issued on
+// (a cudaStream_t passed as void*; nullptr = the legacy default stream).
+void setCudaStream(void *cuda_stream);
+void *getCudaStream();
+
+namespace detail
+{
+// Translates a CUDA runtime status (an int to keep CUDA headers out of user
+// code) into the library's exception.
+void cudaCheck(int status, const char *file, int line);
+}
+
+#define acroCudaErrorCheck(call) ::acro::detail::cudaCheck(static_cast<int>(call), __FILE__, __LINE__)
+
+}
+
+#endif

@@ -1,0 +1,195 @@
+/*
+ * acro_b200.h — C ABI of the B200 (sm_100a) contraction library.
+ *
+ * Plain C: pointers, sizes and integer status codes only.  Two layers:
+ *
+ *  1. KERNEL LAYER (acro_b200_*): one launcher per hand-written kernel family.
+ *     This is the boundary the C++ back end (acro::B200Executor) binds; it
+ *     stands where LLNL/acrotensor's "Cuda" policy calls its run-time generated
+ *     kernel: CudaExecutor::ExecuteSingle / ExecuteMulti
+ *     (exec/CudaExecutor.cpp:36-102) -> CudaKernel::Launch -> cuLaunchKernel
+ *     (util/CudaUtil.cpp:95-103).  All pointers are DEVICE pointers of the
+ *     current device; launches are asynchronous on `stream` (a cudaStream_t
+ *     passed as void*, NULL = legacy default stream).
+ *
+ *  2. ENGINE LAYER (acro_tensor_*, acro_engine_*): handle-based mirror of the
+ *     reference's user API (acro::Tensor, tensor/Tensor.hpp:15-127;
+ *     acro::TensorEngine, kernel/TensorEngine.hpp:26-86) for hosts that cannot
+ *     include C++ headers (ctypes, cgo, JNI ...).  Each function states the
+ *     reference member it corresponds to.
+ *
+ * Every function returns ACRO_B200_OK or a negative status; the text of the
+ * last failure on the calling thread is available from acro_b200_last_error().
+ * Nothing here runs on the CPU: when no CUDA device is usable the compute
+ * entry points fail with ACRO_B200_ECUDA.
+ */
+#ifndef ACRO_B200_H
+#define ACRO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ACRO_B200_OK 0
+#define ACRO_B200_EINVAL (-1)       /* bad argument / failed precondition (an exception in the C++ API) */
+#define ACRO_B200_EUNSUPPORTED (-2) /* the family has no instantiation for these sizes */
+#define ACRO_B200_ECUDA (-3)        /* CUDA runtime failure, or no device */
+#define ACRO_B200_ETIMEOUT (-4)     /* a bounded device-side wait gave up */
+
+#define ACRO_B200_MAX_LOOPS 24
+#define ACRO_B200_MAX_INPUTS 12
+
+/* assignment operators of a contraction string (kernel/TensorKernel.cpp:120-139) */
+#define ACRO_B200_OP_ASSIGN 0 /* "="  */
+#define ACRO_B200_OP_ADD 1    /* "+=" */
+#define ACRO_B200_OP_SUB 2    /* "-=" */
+
+const char *acro_b200_last_error(void);
+
+/* Number of usable CUDA devices (0 when there is none).  Replaces acro::isCudaReady(),
+ * util/CudaUtil.hpp:175-184. */
+int acro_b200_device_count(void);
+
+/* ---------------------------------------------------------------- kernel layer */
+
+/* Aout[i] = val / Aout[i] *= c.  Replace CudaSet / CudaMult, util/CudaUtil.cpp:123-140. */
+int acro_b200_fill(double *data, int64_t n, double val, void *stream);
+int acro_b200_scale(double *data, int64_t n, double c, void *stream);
+
+/*
+ * Generic contraction: any string the parser accepts.
+ * Loops 0..n_outer-1 are the non-contracted loops (ordered so that the last
+ * one is the output's fastest dimension), the remaining loops are the
+ * contracted ones in the reference's summation order.  `*_step[l]` is the
+ * element stride of that variable when loop l advances by one (0 when the
+ * variable does not carry the loop; the sum of both strides for B_i_i).
+ * One thread per output entry; terms are multiplied left to right and added
+ * one by one without fused multiply-add, exactly as
+ * exec/CPUInterpretedExecutor.hpp:58-77 does, so "=" results are bit-identical
+ * to the reference's CPU executor.  Replaces the generated kernel of
+ * exec/CudaExecutor.cpp:111-190 for shapes no specialised family covers.
+ */
+typedef struct acro_b200_generic_desc
+{
+    int32_t n_loops;
+    int32_t n_outer;
+    int32_t n_inputs;
+    int32_t op;
+    int64_t extent[ACRO_B200_MAX_LOOPS];
+    int64_t out_step[ACRO_B200_MAX_LOOPS];
+    int64_t in_step[ACRO_B200_MAX_INPUTS][ACRO_B200_MAX_LOOPS];
+} acro_b200_generic_desc;
+
+int acro_b200_generic_launch(const acro_b200_generic_desc *desc, double *out,
+                             const double *const *inputs, void *stream);
+
+/*
+ * reduce_batch:  out[f] (op)= sum_{n<rows} A[n*F + f] * (w ? w[n] : 1),  f < F.
+ * The contracted batch index is the slowest dimension of A (README kernel
+ * "S_i_j = A_n_i_j B_n").  Streams A once (8*F + 8 bytes per row), keeps
+ * per-thread partial sums, and combines them in a fixed order, so results are
+ * reproducible run to run.  `scratch` is device memory of at least
+ * acro_b200_reduce_batch_scratch_bytes(F) bytes that the call may overwrite;
+ * calls sharing one scratch buffer must not overlap on the device.
+ * Replaces the generated kernel (one 64-thread block for this shape,
+ * exec/CudaExecutor.cpp:193-204).
+ */
+size_t acro_b200_reduce_batch_scratch_bytes(int F);
+int acro_b200_reduce_batch_supported(int64_t rows, int F);
+int acro_b200_reduce_batch(const double *A, const double *w, double *out, int64_t rows, int F,
+                           int op, double *scratch, size_t scratch_bytes, void *stream);
+
+/*
+ * pointwise_sym:  D[p,m,n] (op)= s[p] * sum_{l<dim} X[p,m,l] * Y[p,n,l],   m,n,l < dim,
+ * where s[p] is the left-to-right product of n_scalars point-wise factors
+ * (diffusion geometric factors "D_e_k_m_n = W_k DetJ_e_k Jinv_e_k_m_l Jinv_e_k_n_l").
+ * A point p is a tuple over n_point_loops leading loops with extents
+ * point_extent[]; scalar factor i sits at sum_j idx[j]*scalar_step[i][j].
+ * X, Y and D hold dim*dim contiguous doubles per point.  Arithmetic follows the
+ * reference order term by term, without fused multiply-add (bit-identical for "=").
+ */
+#define ACRO_B200_MAX_POINT_LOOPS 6
+#define ACRO_B200_MAX_SCALARS 6
+typedef struct acro_b200_pointwise_desc
+{
+    int32_t dim;
+    int32_t op;
+    int32_t n_point_loops;
+    int32_t n_scalars;
+    int64_t point_extent[ACRO_B200_MAX_POINT_LOOPS];
+    int64_t scalar_step[ACRO_B200_MAX_SCALARS][ACRO_B200_MAX_POINT_LOOPS];
+} acro_b200_pointwise_desc;
+
+int acro_b200_pointwise_sym_supported(const acro_b200_pointwise_desc *desc);
+int acro_b200_pointwise_sym(const acro_b200_pointwise_desc *desc, const double *const *scalars,
+                            const double *X, const double *Y, double *D, void *stream);
+
+/* ---------------------------------------------------------------- engine layer */
+
+typedef struct acro_tensor acro_tensor;   /* an acro::Tensor */
+typedef struct acro_engine acro_engine;   /* an acro::TensorEngine */
+
+/* Tensor(dims, hdata, ddata, ongpu), tensor/Tensor.hpp:19-42.  hdata NULL = library-owned host buffer. */
+int acro_tensor_create(int rank, const int *dims, double *hdata, double *ddata, int ongpu, acro_tensor **out);
+/* SliceTensor(parent, i0, ...), tensor/SliceTensor.hpp:14-57.  The parent must outlive the slice. */
+int acro_tensor_slice(acro_tensor *parent, int n_indices, const int *indices, acro_tensor **out);
+int acro_tensor_destroy(acro_tensor *t);
+int acro_tensor_rank(const acro_tensor *t);
+int64_t acro_tensor_size(const acro_tensor *t);
+int acro_tensor_dim(const acro_tensor *t, int d);
+double *acro_tensor_data(const acro_tensor *t);         /* GetData */
+double *acro_tensor_device_data(const acro_tensor *t);  /* GetDeviceData */
+int acro_tensor_is_on_gpu(const acro_tensor *t);
+int acro_tensor_is_mapped_to_gpu(const acro_tensor *t);
+int acro_tensor_map_to_gpu(acro_tensor *t);
+int acro_tensor_move_to_gpu(acro_tensor *t);
+int acro_tensor_switch_to_gpu(acro_tensor *t);
+int acro_tensor_unmap_from_gpu(acro_tensor *t);
+int acro_tensor_move_from_gpu(acro_tensor *t);
+int acro_tensor_switch_from_gpu(acro_tensor *t);
+int acro_tensor_set(acro_tensor *t, double val);
+int acro_tensor_mult(acro_tensor *t, double c);
+int acro_tensor_reshape(acro_tensor *t, int rank, const int *dims);
+int acro_tensor_retarget(acro_tensor *t, double *hdata, double *ddata);
+int acro_tensor_set_transient(acro_tensor *t, int transient);
+
+/* TensorEngine(exec_type), kernel/TensorEngine.cpp:27-48. */
+int acro_engine_create(const char *exec_type, acro_engine **out);
+int acro_engine_destroy(acro_engine *e);
+int acro_engine_set_executor_type(acro_engine *e, const char *exec_type);
+int acro_engine_exec_type(acro_engine *e, char *buf, size_t buf_len);
+/* TE(kernel, out, inputs), kernel/TensorEngine.cpp:290-315. */
+int acro_engine_contract(acro_engine *e, const char *kernel, acro_tensor *out, int n_inputs,
+                         acro_tensor *const *inputs);
+/* GetImplementation(kernel, out, inputs); the text is truncated to buf_len-1 characters. */
+int acro_engine_implementation(acro_engine *e, const char *kernel, acro_tensor *out, int n_inputs,
+                               acro_tensor *const *inputs, char *buf, size_t buf_len);
+/* BeginMultiKernelLaunch / EndMultiKernelLaunch, kernel/TensorEngine.cpp:318-336. */
+int acro_engine_begin_multi(acro_engine *e);
+int acro_engine_end_multi(acro_engine *e);
+/* Ends the recording and returns the description of the fused plan instead of running it. */
+int acro_engine_end_multi_describe(acro_engine *e, char *buf, size_t buf_len);
+int acro_engine_clear(acro_engine *e);
+/* cudaStream_t as void*; applies to later launches of this engine. */
+int acro_engine_set_stream(acro_engine *e, void *stream);
+/* Library-wide stream used by tensor copies / fills and by engines without their own. */
+int acro_b200_set_stream(void *stream);
+
+/* Host-only introspection (no device needed): a text dump of the parser's view of a
+ * kernel string — variables, AllIndexNames, ContractionIndexNames
+ * (kernel/TensorKernel.cpp:28-67).  Fails with ACRO_B200_EINVAL on a grammar error. */
+int acro_b200_describe_kernel(const char *kernel, char *buf, size_t buf_len);
+/* Host-only: bind a group of kernels to extents (no data needed) and describe the plan the
+ * "Cuda" back end would run: loop order, shared-outer loops, unique variables, chosen
+ * family per step.  dims_flat holds, per kernel, the output dims then each input's dims. */
+int acro_b200_describe_plan(int n_kernels, const char *const *kernels, const int *dims_flat,
+                            int transient_intermediates, char *buf, size_t buf_len);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ACRO_B200_H */
