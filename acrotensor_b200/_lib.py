@@ -65,6 +65,8 @@ SIGNATURES = {
     "acro_b200_reduce_batch_scratch_bytes": (_SZ, [_I]),
     "acro_b200_reduce_batch_supported": (_I, [_I64, _I]),
     "acro_b200_reduce_batch": (_I, [_P, _P, _P, _I64, _I, _I, _P, _SZ, _P]),
+    "acro_b200_reduce_batch_noalloc_max_f": (_I, []),
+    "acro_b200_reduce_batch_noalloc": (_I, [_P, _P, _P, _I64, _I, _I, _P]),
     "acro_b200_pointwise_sym_supported": (_I, [ctypes.POINTER(PointwiseDesc)]),
     "acro_b200_pointwise_sym": (_I, [ctypes.POINTER(PointwiseDesc), ctypes.POINTER(_P), _P, _P, _P, _P]),
     "acro_tensor_create": (_I, [_I, ctypes.POINTER(_I), _P, _P, _I, ctypes.POINTER(_P)]),

@@ -10,6 +10,8 @@
 // Algorithmic HBM traffic: 8*F bytes of A and 8 bytes of w per row.
 #include "common.cuh"
 
+#include <mutex>
+
 using namespace acro_b200_detail;
 
 namespace
@@ -19,6 +21,13 @@ constexpr int kMaxThreads = 512;
 constexpr int kMaxGrid = 2048;
 constexpr int kUnroll = 4;
 constexpr size_t kCounterBytes = 256;   // keeps the partial sums 256-byte aligned
+
+// Built-in scratch of the allocation-free entry point: room for rows of up to
+// kNoAllocMaxF entries (256 + 2048*32*8 = 524,544 bytes, held by every GPU that loads
+// the library until the process exits).
+constexpr int kNoAllocMaxF = 32;
+constexpr size_t kNoAllocBytes = kCounterBytes + static_cast<size_t>(kMaxGrid) * kNoAllocMaxF * sizeof(double);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 __host__ __device__ inline int threads_for(int F) { return (kMaxThreads / F) * F; }
 
@@ -214,6 +223,52 @@ int acro_b200_reduce_batch(const double *A, const double *w, double *out, int64_
         else reduce_batch_kernel<false, false><<<g, T, smem, s>>>(args);
     }
     return launch_status("acro_b200_reduce_batch");
+}
+
+int acro_b200_reduce_batch_noalloc_max_f(void) { return kNoAllocMaxF; }
+
+// Same reduction as acro_b200_reduce_batch, for callers that must not allocate device
+// memory: the partial sums and the ticket counter live in g_noalloc_scratch.
+//
+// In host code the name g_noalloc_scratch is only a host-side handle of the symbol, not a
+// device address, so the address is looked up with cudaGetSymbolAddress, once per device
+// and with that device current, the first time this function runs on the device.  That
+// first call should therefore happen before any stream capture begins.  Later calls only
+// read the cached address.
+//
+// The function itself calls no cudaMalloc / cudaFree and no allocating library routine.
+// All calls on one GPU share the one scratch array, which still holds the previous call's
+// partial sums: the ticket counter is cleared on the stream before every launch, the
+// partial sums are fully rewritten before they are read.  Two calls that overlap on the
+// same GPU (different streams, or different host threads without ordering) race on it.
+int acro_b200_reduce_batch_noalloc(const double *A, const double *w, double *out, int64_t rows, int F, int op, void *stream)
+{
+    if (F < 1 || F > kNoAllocMaxF)
+    {
+        return fail_unsupported("acro_b200_reduce_batch_noalloc: row length " + std::to_string(F) +
+                                " exceeds the built-in scratch (at most " + std::to_string(kNoAllocMaxF) +
+                                " entries per row); use acro_b200_reduce_batch with caller-provided scratch");
+    }
+    constexpr int kMaxDevices = 64;
+    static std::mutex lock;
+    static double *scratch_of_device[kMaxDevices] = {nullptr};
+    int dev = -1;
+    cudaError_t status = cudaGetDevice(&dev);
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_reduce_batch_noalloc (cudaGetDevice)");
+    if (dev < 0 || dev >= kMaxDevices) return fail_invalid("acro_b200_reduce_batch_noalloc: device ordinal out of range");
+    double *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(lock);
+        if (scratch_of_device[dev] == nullptr)
+        {
+            void *ptr = nullptr;
+            status = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+            if (status != cudaSuccess) return fail_cuda(status, "acro_b200_reduce_batch_noalloc (cudaGetSymbolAddress)");
+            scratch_of_device[dev] = static_cast<double *>(ptr);
+        }
+        scratch = scratch_of_device[dev];
+    }
+    return acro_b200_reduce_batch(A, w, out, rows, F, op, scratch, kNoAllocBytes, stream);
 }
 
 }

@@ -103,6 +103,28 @@ int acro_b200_reduce_batch(const double *A, const double *w, double *out, int64_
                            int op, double *scratch, size_t scratch_bytes, void *stream);
 
 /*
+ * reduce_batch without any allocation.  No counterpart in the reference.
+ * Some callers cannot obtain device memory at the point where they need this reduction:
+ * a plug-in inside an application that owns the whole device memory pool and forbids
+ * allocations in its time-step loop, an in-situ component whose memory budget was fixed at
+ * start-up, or a host library that is handed device pointers but must not call cudaMalloc
+ * itself (an allocation can synchronise the whole device).  For them the partial sums and the ticket
+ * counter live in a static device array inside the library (524,544 bytes per GPU, kept
+ * until the process exits) instead of a caller-provided scratch buffer; inputs and the
+ * output are still the caller's.  Limits and rules:
+ *   - rows of at most acro_b200_reduce_batch_noalloc_max_f() = 32 entries, otherwise
+ *     ACRO_B200_EUNSUPPORTED (use acro_b200_reduce_batch with your own scratch);
+ *   - the first call on each device looks up the array's device address (a one-time
+ *     set-up, done with that device current); make that call before any stream capture;
+ *   - every call on a GPU shares the one array, so calls that overlap on that GPU race:
+ *     keep them on one stream or order them yourself.
+ * Results are identical to acro_b200_reduce_batch's.
+ */
+int acro_b200_reduce_batch_noalloc_max_f(void);
+int acro_b200_reduce_batch_noalloc(const double *A, const double *w, double *out, int64_t rows, int F,
+                                   int op, void *stream);
+
+/*
  * pointwise_sym:  D[p,m,n] (op)= s[p] * sum_{l<dim} X[p,m,l] * Y[p,n,l],   m,n,l < dim,
  * where s[p] is the left-to-right product of n_scalars point-wise factors
  * (diffusion geometric factors "D_e_k_m_n = W_k DetJ_e_k Jinv_e_k_m_l Jinv_e_k_n_l").
