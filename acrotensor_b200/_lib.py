@@ -59,6 +59,7 @@ _S = ctypes.c_char_p
 SIGNATURES = {
     "acro_b200_last_error": (_S, []),
     "acro_b200_device_count": (_I, []),
+    "acro_b200_device_status": (_I, []),
     "acro_b200_fill": (_I, [_P, _I64, _D, _P]),
     "acro_b200_scale": (_I, [_P, _I64, _D, _P]),
     "acro_b200_generic_launch": (_I, [ctypes.POINTER(GenericDesc), _P, ctypes.POINTER(_P), _P]),
@@ -69,6 +70,12 @@ SIGNATURES = {
     "acro_b200_reduce_batch_noalloc": (_I, [_P, _P, _P, _I64, _I, _I, _P]),
     "acro_b200_pointwise_sym_supported": (_I, [ctypes.POINTER(PointwiseDesc)]),
     "acro_b200_pointwise_sym": (_I, [ctypes.POINTER(PointwiseDesc), ctypes.POINTER(_P), _P, _P, _P, _P]),
+    "acro_b200_rank1_gemm_supported": (_I, [_I, _I, _I]),
+    "acro_b200_rank1_gemm": (_I, [_P, _P, _P, _P, _I64, _I, _I, _I, _I, _P]),
+    "acro_b200_batched_gemm_supported": (_I, [_I, _I, _I]),
+    "acro_b200_batched_gemm": (_I, [_P, _P, _P, _I64, _I, _I, _I, _I, _P]),
+    "acro_b200_sumfact_mass_supported": (_I, [_I, _I]),
+    "acro_b200_sumfact_mass": (_I, [_P, _P, _P, _P, _I64, _I, _I, _P]),
     "acro_tensor_create": (_I, [_I, ctypes.POINTER(_I), _P, _P, _I, ctypes.POINTER(_P)]),
     "acro_tensor_slice": (_I, [_P, _I, ctypes.POINTER(_I), ctypes.POINTER(_P)]),
     "acro_tensor_destroy": (_I, [_P]),

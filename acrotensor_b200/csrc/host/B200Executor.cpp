@@ -130,6 +130,27 @@ void B200Executor::Run(std::vector<Tensor *> &outputs, std::vector<std::vector<T
                           "pointwise_sym");
                 break;
             }
+            case plan::Family::Rank1Gemm:
+            {
+                check_abi(acro_b200_rank1_gemm(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), ins[2]->GetDeviceData(),
+                                               out->GetDeviceData(), s.rows, s.sizes[0], s.sizes[1], s.sizes[2], s.op, stream),
+                          "rank1_gemm");
+                break;
+            }
+            case plan::Family::BatchedGemm:
+            {
+                check_abi(acro_b200_batched_gemm(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), out->GetDeviceData(), s.rows,
+                                                 s.sizes[0], s.sizes[1], s.sizes[2], s.op, stream),
+                          "batched_gemm");
+                break;
+            }
+            case plan::Family::SumfactMass:
+            {
+                check_abi(acro_b200_sumfact_mass(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), ins[2]->GetDeviceData(),
+                                                 out->GetDeviceData(), s.rows, s.sizes[0], s.sizes[1], stream),
+                          "sumfact_mass");
+                break;
+            }
             default:
                 ACROBATIC_ASSERT(false, "Planned a kernel family that is not built into this library.");
         }

@@ -242,11 +242,208 @@ bool plan_pointwise_sym(DimensionedKernel &k, int ki, Step &s)
     return true;
 }
 
+// ---------------------------------------------------------------- rank1_gemm
+// M_e_i_j = W_e_q B1_q_i B2_q_j (the three inputs in any order).
+bool plan_rank1_gemm(DimensionedKernel &k, int ki, Step &s)
+{
+    const Names out = k.OutputVar.IndexNames;
+    if (out.size() != 3 || !distinct(out) || k.ContractionIndexNames.size() != 1 || k.GetNumInputVars() != 3) return false;
+    const std::string e = out[0], i = out[1], j = out[2], q = k.ContractionIndexNames[0];
+    int w = -1, b1 = -1, b2 = -1;
+    for (int vari = 0; vari < 3; ++vari)
+    {
+        const Names idx = indices_of(k, vari);
+        if (idx == Names{e, q} && w < 0) w = vari;
+        else if (idx == Names{q, i} && b1 < 0) b1 = vari;
+        else if (idx == Names{q, j} && b2 < 0) b2 = vari;
+        else return false;
+    }
+    if (w < 0 || b1 < 0 || b2 < 0) return false;
+    const std::int64_t elements = extent_of(k, e), nq = extent_of(k, q), ni = extent_of(k, i), nj = extent_of(k, j);
+    if (elements < 32 || !acro_b200_rank1_gemm_supported(static_cast<int>(nq), static_cast<int>(ni), static_cast<int>(nj))) return false;
+    s = Step();
+    s.family = Family::Rank1Gemm;
+    s.kernels = {ki};
+    s.out.ki = ki;
+    s.op = op_code(k);
+    s.rows = elements;
+    s.sizes[0] = static_cast<int>(nq);
+    s.sizes[1] = static_cast<int>(ni);
+    s.sizes[2] = static_cast<int>(nj);
+    for (int vari : {w, b1, b2})
+    {
+        TensorRef r;
+        r.ki = ki;
+        r.vari = vari;
+        s.ins.push_back(r);
+    }
+    s.bytes = io_bytes(k);
+    s.flops = 2 * elements * nq * ni * nj;   // GEMM form
+    std::ostringstream note;
+    note << "GEMM view [" << elements << " x " << nq << "] x [" << nq << " x " << ni * nj
+         << "], right operand formed on the fly, fp64 tensor cores (mma.sync m8n8k4)";
+    s.note = note.str();
+    return true;
+}
+
+// ---------------------------------------------------------------- batched_gemm
+// C_e_i_j = A_e_i_k B_e_k_j (either operand order).
+bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
+{
+    const Names out = k.OutputVar.IndexNames;
+    if (out.size() != 3 || !distinct(out) || k.ContractionIndexNames.size() != 1 || k.GetNumInputVars() != 2) return false;
+    const std::string e = out[0], i = out[1], j = out[2], kk = k.ContractionIndexNames[0];
+    int av = -1, bv = -1;
+    for (int vari = 0; vari < 2; ++vari)
+    {
+        const Names idx = indices_of(k, vari);
+        if (idx == Names{e, i, kk} && av < 0) av = vari;
+        else if (idx == Names{e, kk, j} && bv < 0) bv = vari;
+        else return false;
+    }
+    if (av < 0 || bv < 0) return false;
+    const std::int64_t batch = extent_of(k, e), m = extent_of(k, i), n = extent_of(k, j), kn = extent_of(k, kk);
+    if (!acro_b200_batched_gemm_supported(static_cast<int>(m), static_cast<int>(n), static_cast<int>(kn))) return false;
+    s = Step();
+    s.family = Family::BatchedGemm;
+    s.kernels = {ki};
+    s.out.ki = ki;
+    s.op = op_code(k);
+    s.rows = batch;
+    s.sizes[0] = static_cast<int>(m);
+    s.sizes[1] = static_cast<int>(n);
+    s.sizes[2] = static_cast<int>(kn);
+    TensorRef a, b;
+    a.ki = b.ki = ki;
+    a.vari = av;
+    b.vari = bv;
+    s.ins = {a, b};
+    s.bytes = io_bytes(k);
+    s.flops = 2 * batch * m * n * kn;
+    std::ostringstream note;
+    note << batch << " products of " << m << "x" << kn << " by " << kn << "x" << n
+         << ", persistent CTAs, 3-stage asynchronous bulk-copy ring, fp64 tensor cores (mma.sync m8n8k4)";
+    s.note = note.str();
+    return true;
+}
+
+// ---------------------------------------------------------------- sumfact_mass
+// A kernel group is recognised by its shape, not by its names: variables and indices are
+// renamed in order of first appearance and the result is compared with the same renaming of
+// the sum-factorised mass operator chain.
+std::string canonical_form(const std::vector<DimensionedKernel *> &kernels)
+{
+    std::vector<std::string> vars, idxs;
+    auto id_of = [](std::vector<std::string> &table, const std::string &name) {
+        auto it = std::find(table.begin(), table.end(), name);
+        if (it == table.end())
+        {
+            table.push_back(name);
+            return table.size() - 1;
+        }
+        return static_cast<std::size_t>(it - table.begin());
+    };
+    std::ostringstream os;
+    for (DimensionedKernel *k : kernels)
+    {
+        for (int vari = -1; vari < k->GetNumInputVars(); ++vari)
+        {
+            os << "V" << id_of(vars, k->GetVarName(vari));
+            for (const std::string &idx : indices_of(*k, vari)) os << "_x" << id_of(idxs, idx);
+            if (vari < 0) os << k->EqOperator;
+            else os << " ";
+        }
+        os << ";";
+    }
+    return os.str();
+}
+
+const char *const kMassChain[6] = {
+    "T1_e_i1_i2_k3 = B_k3_i3 U_e_i1_i2_i3",  "T2_e_i1_k2_k3 = B_k2_i2 T1_e_i1_i2_k3", "X_e_k1_k2_k3 = B_k1_i1 T2_e_i1_k2_k3 W_e_k1_k2_k3",
+    "Y1_e_i1_k2_k3 = B_k1_i1 X_e_k1_k2_k3", "Y2_e_i1_i2_k3 = B_k2_i2 Y1_e_i1_k2_k3", "V_e_i1_i2_i3 = B_k3_i3 Y2_e_i1_i2_k3"};
+
+std::string canonical_text_form(const char *const *texts, int n)
+{
+    // Same renaming applied to plain strings (the pattern has no tensors attached).
+    std::vector<std::string> vars, idxs;
+    auto id_of = [](std::vector<std::string> &table, const std::string &name) {
+        auto it = std::find(table.begin(), table.end(), name);
+        if (it == table.end())
+        {
+            table.push_back(name);
+            return table.size() - 1;
+        }
+        return static_cast<std::size_t>(it - table.begin());
+    };
+    std::ostringstream os;
+    for (int i = 0; i < n; ++i)
+    {
+        TensorKernel k(texts[i]);
+        for (int vari = -1; vari < k.GetNumInputVars(); ++vari)
+        {
+            os << "V" << id_of(vars, k.GetVarName(vari));
+            const Names &names = vari < 0 ? k.OutputVar.IndexNames : k.InputVars[vari].IndexNames;
+            for (const std::string &idx : names) os << "_x" << id_of(idxs, idx);
+            if (vari < 0) os << k.EqOperator;
+            else os << " ";
+        }
+        os << ";";
+    }
+    return os.str();
+}
+
+bool plan_sumfact_mass(DimensionedMultiKernel &mk, Step &s)
+{
+    if (mk.GetNumKernels() != 6) return false;
+    static const std::string pattern = canonical_text_form(kMassChain, 6);
+    if (canonical_form(mk.Kernels) != pattern) return false;
+    DimensionedKernel &first = *mk.Kernels[0];   // T1_e_i1_i2_k3 = B_k3_i3 U_e_i1_i2_i3
+    DimensionedKernel &third = *mk.Kernels[2];   // X_e_k1_k2_k3 = B_k1_i1 T2_e_i1_k2_k3 W_e_k1_k2_k3
+    const Names u = indices_of(first, 1), x = indices_of(third, -1);
+    const std::int64_t elements = extent_of(first, u[0]);
+    const std::int64_t p = extent_of(first, u[1]), q = extent_of(third, x[1]);
+    for (int d = 1; d < 4; ++d)
+    {
+        if (extent_of(first, u[d]) != p || extent_of(third, x[d]) != q) return false;
+    }
+    if (!acro_b200_sumfact_mass_supported(static_cast<int>(p), static_cast<int>(q))) return false;
+
+    s = Step();
+    s.family = Family::SumfactMass;
+    s.kernels = {0, 1, 2, 3, 4, 5};
+    s.op = ACRO_B200_OP_ASSIGN;
+    s.rows = elements;
+    s.sizes[0] = static_cast<int>(p);
+    s.sizes[1] = static_cast<int>(q);
+    s.out.ki = 5;                       // V
+    TensorRef b, uu, w;
+    b.ki = 0; b.vari = 0;               // B
+    uu.ki = 0; uu.vari = 1;             // U
+    w.ki = 2; w.vari = 2;               // W
+    s.ins = {b, uu, w};
+    for (int ki = 0; ki < 5; ++ki)
+    {
+        TensorRef r;
+        r.ki = ki;
+        s.elided.push_back(r);
+    }
+    s.bytes = elements * 8 * (2 * p * p * p + q * q * q) + 8 * p * q;
+    // as written: one multiply-add per term of every stage, plus the extra factor W in stage three
+    s.flops = elements * (2 * (p * p * q * p + p * q * q * p + q * q * q * p + p * q * q * q + p * p * q * q + p * p * p * q) + q * q * q * p);
+    std::ostringstream note;
+    note << "six stages fused, " << elements << " elements, p=" << p << " q=" << q
+         << "; intermediates in registers/shared memory, operands by asynchronous bulk copy";
+    s.note = note.str();
+    return true;
+}
+
 Step plan_single(DimensionedKernel &k, int ki)
 {
     Step s;
     if (plan_reduce_batch(k, ki, s)) return s;
     if (plan_pointwise_sym(k, ki, s)) return s;
+    if (plan_rank1_gemm(k, ki, s)) return s;
+    if (plan_batched_gemm(k, ki, s)) return s;
     return plan_generic(k, ki);
 }
 
@@ -268,8 +465,17 @@ const char *FamilyName(Family f)
 
 Program BuildProgram(DimensionedMultiKernel &mk, bool allow_elision)
 {
-    (void)allow_elision;
     Program p;
+    if (allow_elision)
+    {
+        Step fused;
+        if (plan_sumfact_mass(mk, fused))
+        {
+            p.steps.push_back(fused);
+            p.elides = true;
+            return p;
+        }
+    }
     for (int ki = 0; ki < mk.GetNumKernels(); ++ki)
     {
         p.steps.push_back(plan_single(*mk.Kernels[ki], ki));

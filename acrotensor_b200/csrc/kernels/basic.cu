@@ -1,5 +1,6 @@
 // Status plumbing, device discovery, fill and scale.
 #include "common.cuh"
+#include "tma.cuh"
 
 #include <mutex>
 #include <vector>
@@ -48,6 +49,28 @@ int sm_count()
 
 }
 
+static __device__ int g_wait_timed_out = 0;
+
+namespace acro_b200_detail
+{
+int *wait_flag_device_ptr()
+{
+    constexpr int kMaxDevices = 64;
+    static std::mutex lock;
+    static int *ptr_of_device[kMaxDevices] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> guard(lock);
+    if (ptr_of_device[dev] == nullptr)
+    {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_wait_timed_out) != cudaSuccess) return nullptr;
+        ptr_of_device[dev] = static_cast<int *>(p);
+    }
+    return ptr_of_device[dev];
+}
+}
+
 using namespace acro_b200_detail;
 
 namespace
@@ -87,6 +110,24 @@ int acro_b200_device_count(void)
         return 0;
     }
     return n;
+}
+
+int acro_b200_device_status(void)
+{
+    // Blocks until the device is idle, then reads (and clears) the bounded-wait flag.
+    cudaError_t status = cudaDeviceSynchronize();
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_device_status");
+    int flag = 0;
+    status = cudaMemcpyFromSymbol(&flag, g_wait_timed_out, sizeof flag);
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_device_status");
+    if (flag != 0)
+    {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_wait_timed_out, &zero, sizeof zero);
+        set_last_error("a bounded device-side wait on an asynchronous copy gave up; results of that launch are invalid");
+        return ACRO_B200_ETIMEOUT;
+    }
+    return ACRO_B200_OK;
 }
 
 int acro_b200_fill(double *data, int64_t n, double val, void *stream)

@@ -20,6 +20,10 @@ int fail_cuda(cudaError_t status, const char *where);
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Device address of the per-device flag a kernel raises when one of its bounded waits gave
+// up (nullptr on failure); acro_b200_device_status() reads and clears it.
+int *wait_flag_device_ptr();
+
 inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
 
 // To be called right after a kernel launch.

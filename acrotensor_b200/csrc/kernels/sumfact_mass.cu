@@ -1,0 +1,274 @@
+// sumfact_mass: the six-stage sum-factorised 3D mass operator, fused into one kernel.
+//
+//   T1_e_i1_i2_k3 = B_k3_i3 U_e_i1_i2_i3        Y1_e_i1_k2_k3 = B_k1_i1 X_e_k1_k2_k3
+//   T2_e_i1_k2_k3 = B_k2_i2 T1_e_i1_i2_k3       Y2_e_i1_i2_k3 = B_k2_i2 Y1_e_i1_k2_k3
+//   X_e_k1_k2_k3  = B_k1_i1 T2_e_i1_k2_k3 W_e_k1_k2_k3      V_e_i1_i2_i3 = B_k3_i3 Y2_e_i1_i2_k3
+//
+// Only U, W (read) and V (written) touch HBM: 8*(P^3 + Q^3 + P^3) = 2024 bytes per element
+// for P = 4 dofs, Q = 5 quadrature points per direction; T1, T2, X, Y1 live in registers and
+// Y2 crosses threads once through shared memory.
+//
+// Work split: Q threads per element.  Thread (e, k3) owns the k3-plane: stages 1-5 contract
+// i3, i2, i1, k1, k2 entirely in its registers (U is read from shared memory, the Q threads
+// of an element reading the same address in the same instruction: a broadcast).  Stage 6
+// contracts k3, which crosses the plane owners: Y2 goes through shared memory and thread
+// (e, i1) finishes V_e_i1_*_*.  Tiles of 32 elements; U and W tiles arrive by asynchronous
+// bulk copies (per element for U, into slots padded to 66 doubles so that the elements of a
+// warp fall into different banks; one span for W), issued as soon as the previous tile's
+// copies are dead, so they overlap the rest of that tile and the other CTA of the SM.
+#include "common.cuh"
+#include "tma.cuh"
+
+using namespace acro_b200_detail;
+
+namespace
+{
+
+constexpr int P = 4;
+constexpr int Q = 5;
+constexpr int ET = 32;                    // elements per tile
+constexpr int NT = ET * Q;                // threads per CTA
+constexpr int U_ELEM = P * P * P;         // 64
+constexpr int W_ELEM = Q * Q * Q;         // 125
+constexpr int U_STRIDE = U_ELEM + 2;      // padded slot, 16-byte multiple
+constexpr int Y_STRIDE = P * P * Q + 5;   // 85: conflict-free for both access patterns
+constexpr int V_ROW = P * P + 2;          // 18 doubles per (element, i1) row
+
+struct Smem
+{
+    double U[ET * U_STRIDE];
+    double W[ET * W_ELEM];
+    double Y[ET * Y_STRIDE];
+    double V[ET * P * V_ROW];
+    double B[Q * P];
+    uint64_t bar;
+};
+
+struct MassArgs
+{
+    const double *B;
+    const double *U;
+    const double *W;
+    double *V;
+    int64_t elements;
+    int *wait_flag;
+    int use_bulk;   // operands are 16-byte aligned: bulk copies allowed
+};
+
+__device__ __forceinline__ void issue_tile_load(Smem &s, const MassArgs &a, int64_t tile, int64_t n_tiles_full)
+{
+    // Only whole tiles travel by bulk copy (sizes and addresses stay 16-byte multiples).
+    if (!a.use_bulk || tile >= n_tiles_full) return;
+    if (threadIdx.x < 32)
+    {
+        const int64_t e0 = tile * ET;
+        if (threadIdx.x == 0) mbar_arrive_expect_tx(&s.bar, ET * (U_ELEM + W_ELEM) * 8);
+        __syncwarp();
+        bulk_load(s.U + threadIdx.x * U_STRIDE, a.U + (e0 + threadIdx.x) * U_ELEM, U_ELEM * 8, &s.bar);
+        if (threadIdx.x == 0) bulk_load(s.W, a.W + e0 * W_ELEM, ET * W_ELEM * 8, &s.bar);
+    }
+}
+
+__global__ void __launch_bounds__(NT, 2)
+sumfact_mass_kernel(const MassArgs a)
+{
+    extern __shared__ __align__(128) unsigned char raw[];
+    Smem &s = *reinterpret_cast<Smem *>(raw);
+    const int tid = threadIdx.x;
+    const int64_t n_tiles = (a.elements + ET - 1) / ET;
+    const int64_t n_tiles_full = a.elements / ET;
+
+    if (tid == 0)
+    {
+        mbar_init(&s.bar, 1);
+        fence_mbar_init();
+    }
+    if (tid < Q * P) s.B[tid] = a.B[tid];
+    __syncthreads();
+
+    double Bm[Q][P];   // B_k_i
+#pragma unroll
+    for (int k = 0; k < Q; ++k)
+#pragma unroll
+        for (int i = 0; i < P; ++i) Bm[k][i] = s.B[k * P + i];
+
+    // plane ownership (stages 1-5) and row ownership (stage 6)
+    const int eb = tid / Q, k3 = tid % Q;
+    const int ec = tid / P, i1c = tid % P;
+    double brow[P];   // B_k3_*
+#pragma unroll
+    for (int i = 0; i < P; ++i) brow[i] = s.B[k3 * P + i];
+
+    uint32_t parity = 0;
+    int64_t tile = blockIdx.x;
+    issue_tile_load(s, a, tile, n_tiles_full);
+
+    for (; tile < n_tiles; tile += gridDim.x)
+    {
+        const int64_t e0 = tile * ET;
+        const int64_t left = a.elements - e0;
+        const int n_e = left < ET ? static_cast<int>(left) : ET;
+
+        if (a.use_bulk && tile < n_tiles_full)
+        {
+            if (!mbar_wait(&s.bar, parity)) atomicExch(a.wait_flag, 1);
+            parity ^= 1u;
+        }
+        else
+        {
+            // ragged or unaligned tile: plain coalesced loads into the same layout
+            for (int i = tid; i < n_e * U_ELEM; i += NT) s.U[(i / U_ELEM) * U_STRIDE + (i % U_ELEM)] = __ldcs(a.U + e0 * U_ELEM + i);
+            for (int i = tid; i < n_e * W_ELEM; i += NT) s.W[i] = __ldcs(a.W + e0 * W_ELEM + i);
+            __syncthreads();
+        }
+
+        if (eb < n_e)
+        {
+            const double *u = s.U + eb * U_STRIDE;
+            // stage 1: T1_i1_i2 (this k3) = sum_i3 B_k3_i3 U_i1_i2_i3
+            double t1[P][P];
+#pragma unroll
+            for (int i1 = 0; i1 < P; ++i1)
+#pragma unroll
+                for (int i2 = 0; i2 < P; ++i2)
+                {
+                    const double2 lo = *reinterpret_cast<const double2 *>(u + (i1 * P + i2) * P);
+                    const double2 hi = *reinterpret_cast<const double2 *>(u + (i1 * P + i2) * P + 2);
+                    double acc = brow[0] * lo.x;
+                    acc = fma(brow[1], lo.y, acc);
+                    acc = fma(brow[2], hi.x, acc);
+                    acc = fma(brow[3], hi.y, acc);
+                    t1[i1][i2] = acc;
+                }
+            // stage 2: T2_i1_k2 = sum_i2 B_k2_i2 T1_i1_i2
+            double t2[P][Q];
+#pragma unroll
+            for (int i1 = 0; i1 < P; ++i1)
+#pragma unroll
+                for (int k2 = 0; k2 < Q; ++k2)
+                {
+                    double acc = Bm[k2][0] * t1[i1][0];
+#pragma unroll
+                    for (int i2 = 1; i2 < P; ++i2) acc = fma(Bm[k2][i2], t1[i1][i2], acc);
+                    t2[i1][k2] = acc;
+                }
+            // stage 3: X_k1_k2 = W_k1_k2_k3 * sum_i1 B_k1_i1 T2_i1_k2
+            double x[Q][Q];
+            const double *w = s.W + eb * W_ELEM + k3;
+#pragma unroll
+            for (int k1 = 0; k1 < Q; ++k1)
+#pragma unroll
+                for (int k2 = 0; k2 < Q; ++k2)
+                {
+                    double acc = Bm[k1][0] * t2[0][k2];
+#pragma unroll
+                    for (int i1 = 1; i1 < P; ++i1) acc = fma(Bm[k1][i1], t2[i1][k2], acc);
+                    x[k1][k2] = acc * w[(k1 * Q + k2) * Q];
+                }
+            // stage 4: Y1_i1_k2 = sum_k1 B_k1_i1 X_k1_k2
+            double y1[P][Q];
+#pragma unroll
+            for (int i1 = 0; i1 < P; ++i1)
+#pragma unroll
+                for (int k2 = 0; k2 < Q; ++k2)
+                {
+                    double acc = Bm[0][i1] * x[0][k2];
+#pragma unroll
+                    for (int k1 = 1; k1 < Q; ++k1) acc = fma(Bm[k1][i1], x[k1][k2], acc);
+                    y1[i1][k2] = acc;
+                }
+            // stage 5: Y2_i1_i2 = sum_k2 B_k2_i2 Y1_i1_k2  -> shared, layout [e][i1][i2][k3]
+            double *y = s.Y + eb * Y_STRIDE + k3;
+#pragma unroll
+            for (int i1 = 0; i1 < P; ++i1)
+#pragma unroll
+                for (int i2 = 0; i2 < P; ++i2)
+                {
+                    double acc = Bm[0][i2] * y1[i1][0];
+#pragma unroll
+                    for (int k2 = 1; k2 < Q; ++k2) acc = fma(Bm[k2][i2], y1[i1][k2], acc);
+                    y[(i1 * P + i2) * Q] = acc;
+                }
+        }
+        __syncthreads();   // U and W of this tile are dead, Y2 is complete
+        issue_tile_load(s, a, tile + gridDim.x, n_tiles_full);
+
+        if (ec < n_e && tid < ET * P)
+        {
+            // stage 6: V_i1_i2_i3 = sum_k3 B_k3_i3 Y2_i1_i2_k3
+            const double *y = s.Y + ec * Y_STRIDE + i1c * P * Q;
+            double *v = s.V + (ec * P + i1c) * V_ROW;
+#pragma unroll
+            for (int i2 = 0; i2 < P; ++i2)
+            {
+                double yv[Q];
+#pragma unroll
+                for (int k = 0; k < Q; ++k) yv[k] = y[i2 * Q + k];
+#pragma unroll
+                for (int i3 = 0; i3 < P; ++i3)
+                {
+                    double acc = Bm[0][i3] * yv[0];
+#pragma unroll
+                    for (int k = 1; k < Q; ++k) acc = fma(Bm[k][i3], yv[k], acc);
+                    v[i2 * P + i3] = acc;
+                }
+            }
+        }
+        __syncthreads();   // V tile complete
+
+        // contiguous coalesced store of the V tile (rows of 16 doubles, padded to 18 in shared memory)
+        double *dst = a.V + e0 * U_ELEM;
+        if (aligned16(a.V))
+        {
+            for (int i2 = tid; i2 < n_e * U_ELEM / 2; i2 += NT)
+            {
+                const int i = 2 * i2;
+                const double2 val = *reinterpret_cast<const double2 *>(s.V + (i / (P * P)) * V_ROW + (i % (P * P)));
+                __stcs(reinterpret_cast<double2 *>(dst + i), val);
+            }
+        }
+        else
+        {
+            for (int i = tid; i < n_e * U_ELEM; i += NT) __stcs(dst + i, s.V[(i / (P * P)) * V_ROW + (i % (P * P))]);
+        }
+        // The next tile writes Y only after every thread passed the first barrier above and V
+        // only after the next first barrier, so no third barrier is needed here.
+    }
+}
+
+}
+
+extern "C" {
+
+int acro_b200_sumfact_mass_supported(int p, int q) { return (p == P && q == Q) ? 1 : 0; }
+
+int acro_b200_sumfact_mass(const double *B, const double *U, const double *W, double *V, int64_t elements, int p, int q, void *stream)
+{
+    if (B == nullptr || U == nullptr || W == nullptr || V == nullptr) return fail_invalid("acro_b200_sumfact_mass: null argument");
+    if (elements < 1) return fail_invalid("acro_b200_sumfact_mass: element count must be positive");
+    if (!acro_b200_sumfact_mass_supported(p, q)) return fail_unsupported("acro_b200_sumfact_mass: only P=4, Q=5 is instantiated");
+    const int sms = sm_count();
+    if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_sumfact_mass");
+
+    MassArgs args;
+    args.B = B;
+    args.U = U;
+    args.W = W;
+    args.V = V;
+    args.elements = elements;
+    args.wait_flag = wait_flag_device_ptr();
+    if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_sumfact_mass (status flag)");
+    args.use_bulk = (aligned16(U) && aligned16(W)) ? 1 : 0;
+
+    const size_t smem = sizeof(Smem);
+    // The opt-in is a per-device function attribute; setting it again is a cheap host call.
+    cudaError_t status = cudaFuncSetAttribute(sumfact_mass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_sumfact_mass (shared memory opt-in)");
+    const int64_t n_tiles = (elements + ET - 1) / ET;
+    int64_t grid = static_cast<int64_t>(sms) * 2;
+    if (grid > n_tiles) grid = n_tiles;
+    sumfact_mass_kernel<<<static_cast<int>(grid), NT, smem, as_stream(stream)>>>(args);
+    return launch_status("acro_b200_sumfact_mass");
+}
+
+}

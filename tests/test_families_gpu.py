@@ -1,0 +1,196 @@
+"""GPU parity of the fp64 tensor-core and fused-chain kernel families (rank1_gemm,
+batched_gemm, sumfact_mass), through the kernel layer of the C ABI and through the engine.
+These families reorder sums and use fused multiply-add / DMMA, so the gate is
+|gpu - ref| <= 1e-12 * sum|terms| (the fp64 tolerance of the benchmark definition)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import acrotensor_b200 as ab
+import gpu_util as gu
+from acrotensor_b200 import _lib
+from acrotensor_b200._lib import check, lib
+from acrotensor_b200.runner import Session, alloc_host
+from acrotensor_b200.workloads import BY_KEY, MASS_CHAIN
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-12
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+    assert torch.cuda.is_available()
+    return torch
+
+
+def to_dev(torch, arr, offset=0):
+    """Device copy of arr; offset=1 puts it on an 8-byte (not 16-byte) boundary."""
+    flat = torch.zeros(arr.size + offset, dtype=torch.float64, device="cuda")
+    flat[offset:] = torch.from_numpy(np.ascontiguousarray(arr).reshape(-1)).cuda()
+    return flat, ctypes.c_void_p(flat.data_ptr() + 8 * offset)
+
+
+def status_ok():
+    assert lib().acro_b200_device_status() == _lib.OK
+
+
+@pytest.mark.parametrize("elements,ni,nj,op,offset", [
+    (32, 27, 27, 0, 0), (33, 27, 27, 0, 0), (1, 27, 27, 0, 0), (100, 27, 27, 1, 0), (257, 27, 27, 2, 0),
+    (64, 5, 7, 0, 0), (95, 32, 32, 0, 0), (70, 27, 27, 0, 1), (10000, 27, 27, 0, 0),
+])
+def test_rank1_gemm_kernel(torch, elements, ni, nj, op, offset):
+    rng = np.random.default_rng(elements + ni)
+    w = rng.random((elements, 64)) + 0.5
+    b1 = rng.random((64, ni)) * 2 - 1
+    b2 = b1 if ni == nj else rng.random((64, nj)) * 2 - 1
+    m0 = rng.random((elements, ni, nj))
+    prod, mags = np.zeros_like(m0), np.zeros_like(m0)
+    oracle.contract("port", "M_e_i_j = W_e_q B_q_i C_q_j", prod, w, b1, b2)
+    oracle.contract("port", "M_e_i_j = W_e_q B_q_i C_q_j", mags, w, np.abs(b1), np.abs(b2))
+    expect = [prod, m0 + prod, m0 - prod][op]
+    keep_w, pw = to_dev(torch, w, offset)
+    keep_1, p1 = to_dev(torch, b1)
+    keep_2, p2 = (keep_1, p1) if b2 is b1 else to_dev(torch, b2)
+    keep_m, pm = to_dev(torch, m0)
+    assert lib().acro_b200_rank1_gemm_supported(64, ni, nj) == 1
+    check(lib().acro_b200_rank1_gemm(pw, p1, p2, pm, elements, 64, ni, nj, op, None))
+    status_ok()
+    got = keep_m.cpu().numpy().reshape(m0.shape)
+    assert oracle.parity_error(got, expect, mags + np.abs(m0)) <= TOL
+
+
+@pytest.mark.parametrize("batch,op,offset", [(1, 0, 0), (2, 1, 0), (5, 2, 0), (3, 0, 1), (500, 0, 0)])
+def test_batched_gemm_kernel(torch, batch, op, offset):
+    rng = np.random.default_rng(batch)
+    a, b = rng.standard_normal((batch, 64, 64)), rng.standard_normal((batch, 64, 64))
+    c0 = rng.random((batch, 64, 64))
+    ka, pa = to_dev(torch, a, offset)
+    kb, pb = to_dev(torch, b)
+    kc, pc = to_dev(torch, c0)
+    check(lib().acro_b200_batched_gemm(pa, pb, pc, batch, 64, 64, 64, op, None))
+    status_ok()
+    got = kc.cpu().numpy().reshape(c0.shape)
+    sample = sorted(set([0, batch // 2, batch - 1]))         # the oracle needs 262144 terms per matrix
+    prod = np.zeros((len(sample), 64, 64))
+    mags = np.zeros_like(prod)
+    oracle.contract("port", "C_e_i_j = A_e_i_k B_e_k_j", prod, a[sample], b[sample])
+    oracle.contract("port", "C_e_i_j = A_e_i_k B_e_k_j", mags, np.abs(a[sample]), np.abs(b[sample]))
+    expect = [prod, c0[sample] + prod, c0[sample] - prod][op]
+    assert oracle.parity_error(got[sample], expect, mags + np.abs(c0[sample])) <= TOL
+    # every matrix against a float64 matmul (looser: numpy's own summation order differs too)
+    ref = np.matmul(a, b)
+    full = [ref, c0 + ref, c0 - ref][op]
+    assert np.max(np.abs(got - full)) <= 1e-11
+
+
+def run_chain_oracle(b, u, w):
+    e = u.shape[0]
+    t = {"B": b, "U": u, "W": w, "T1": np.zeros((e, 4, 4, 5)), "T2": np.zeros((e, 4, 5, 5)), "X": np.zeros((e, 5, 5, 5)),
+         "Y1": np.zeros((e, 4, 5, 5)), "Y2": np.zeros((e, 4, 4, 5)), "V": np.zeros((e, 4, 4, 4))}
+    names = sorted(t)
+    prog = [(k, names.index(o), [names.index(i) for i in ins]) for k, o, ins in MASS_CHAIN]
+    oracle.run("port", [t[n] for n in names], prog, multi=True)
+    return t["V"]
+
+
+@pytest.mark.parametrize("elements,offset", [(1, 0), (31, 0), (32, 0), (33, 0), (1000, 0), (65, 1), (10007, 0)])
+def test_sumfact_mass_kernel(torch, elements, offset):
+    rng = np.random.default_rng(elements)
+    b = rng.random((5, 4)) * 2 - 1
+    u = rng.random((elements, 4, 4, 4)) * 2 - 1
+    w = rng.random((elements, 5, 5, 5)) + 0.5
+    ref = run_chain_oracle(b, u, w)
+    mags = run_chain_oracle(np.abs(b), np.abs(u), w)
+    kb, pb = to_dev(torch, b)
+    ku, pu = to_dev(torch, u, offset)
+    kw, pw = to_dev(torch, w)
+    kv, pv = to_dev(torch, np.full(ref.shape, -1.0))
+    assert lib().acro_b200_sumfact_mass_supported(4, 5) == 1 and lib().acro_b200_sumfact_mass_supported(3, 4) == 0
+    check(lib().acro_b200_sumfact_mass(pb, pu, pw, pv, elements, 4, 5, None))
+    status_ok()
+    got = kv.cpu().numpy().reshape(ref.shape)
+    assert oracle.parity_error(got, ref, mags) <= TOL
+
+
+def test_chain_through_the_engine_fused_and_unfused():
+    w = BY_KEY["cfg2"]
+    batch = 700
+    host_f = alloc_host(w, batch, w.make_inputs(batch, seed=3))
+    host_u = {k: v.copy() for k, v in host_f.items()}
+    fused = Session(w, host_f, transient=True)
+    assert "family=sumfact_mass" in fused.plan_text()
+    fused.run(); fused.fetch()
+    unfused = Session(w, host_u, transient=False)           # reference semantics: everything materialised
+    unfused.run(); unfused.fetch(w.names("out") + w.names("tmp"))
+    ref = run_chain_oracle(host_u["B"], host_u["U"], host_u["W"])
+    mags = run_chain_oracle(np.abs(host_u["B"]), np.abs(host_u["U"]), host_u["W"])
+    assert np.array_equal(host_u["V"], ref)                  # generic kernels: bit-identical, stage by stage
+    assert np.any(host_u["T1"] != 0) and np.all(host_f["T1"] == 0)   # transient intermediates never materialised
+    assert oracle.parity_error(host_f["V"], ref, mags) <= TOL
+    assert lib().acro_b200_device_status() == _lib.OK
+
+
+def test_benchmark_families_through_the_engine():
+    for key, batch, family in (("cfg1", 200, "rank1_gemm"), ("cfg4", 4, "batched_gemm")):
+        w = BY_KEY[key]
+        host = alloc_host(w, batch, w.make_inputs(batch, seed=5))
+        sess = Session(w, host)
+        assert "family=" + family in sess.plan_text()
+        sess.run(); sess.fetch()
+        names = sorted(host)
+        out = w.names("out")[0]
+        got = host[out].copy()
+        prog = [(k, names.index(o), [names.index(i) for i in ins]) for k, o, ins in w.program]
+        mags = [np.abs(host[n]) for n in names]
+        oracle.run("port", [host[n] for n in names], prog)
+        oracle.run("port", mags, prog)
+        assert oracle.parity_error(got, host[out], mags[names.index(out)]) <= TOL
+    assert lib().acro_b200_device_status() == _lib.OK
+
+
+def test_full_size_tensor_core_properties(torch):
+    # cfg 4 at E = 2^14: B_e = identity gives C_e = A_e exactly (products by 1, sums with 0)
+    E = 1 << 14
+    a = torch.randn(E, 64, 64, dtype=torch.float64, device="cuda")
+    b = torch.eye(64, dtype=torch.float64, device="cuda").repeat(E, 1, 1)
+    c = torch.empty_like(a)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    check(lib().acro_b200_batched_gemm(p(a), p(b), p(c), E, 64, 64, 64, 0, None))
+    assert bool((c == a).all())
+    check(lib().acro_b200_batched_gemm(p(b), p(a), p(c), E, 64, 64, 64, 0, None))
+    assert bool((c == a).all())
+    del a, b, c
+    # cfg 1 at E = 2^18: W = 1 makes every element matrix the same Gram matrix; W = 2^k scales exactly
+    E = 1 << 18
+    rng = np.random.default_rng(1)
+    bm = rng.random((64, 27)) * 2 - 1
+    db = torch.from_numpy(bm).cuda()
+    w = torch.ones(E, 64, dtype=torch.float64, device="cuda")
+    w[1::2] = 4.0
+    m = torch.empty(E, 27, 27, dtype=torch.float64, device="cuda")
+    check(lib().acro_b200_rank1_gemm(p(w), p(db), p(db), p(m), E, 64, 27, 27, 0, None))
+    assert bool((m[0::2] == m[0]).all()) and bool((m[1::2] == 4.0 * m[0]).all())
+    ref, mags = np.zeros((1, 27, 27)), np.zeros((1, 27, 27))
+    oracle.contract("port", "M_e_i_j = W_e_q B_q_i B_q_j", ref, np.ones((1, 64)), bm, bm)
+    oracle.contract("port", "M_e_i_j = W_e_q B_q_i B_q_j", mags, np.ones((1, 64)), np.abs(bm), np.abs(bm))
+    assert oracle.parity_error(m[0:1].cpu().numpy(), ref, mags) <= TOL
+    del w, m
+    # cfg 2 at E = 2^20: scaling U by 2 scales V by 2 exactly; a seeded sample matches the oracle
+    E = 1 << 20
+    gen = torch.Generator(device="cuda"); gen.manual_seed(9)
+    bq = torch.rand(5, 4, generator=gen, device="cuda", dtype=torch.float64) * 2 - 1
+    u = torch.rand(E, 4, 4, 4, generator=gen, device="cuda", dtype=torch.float64) * 2 - 1
+    wq = torch.rand(E, 5, 5, 5, generator=gen, device="cuda", dtype=torch.float64) + 0.5
+    v1, v2 = torch.empty_like(u), torch.empty_like(u)
+    check(lib().acro_b200_sumfact_mass(p(bq), p(u), p(wq), p(v1), E, 4, 5, None))
+    u.mul_(2.0)
+    check(lib().acro_b200_sumfact_mass(p(bq), p(u), p(wq), p(v2), E, 4, 5, None))
+    assert bool((v2 == 2.0 * v1).all())
+    take = [0, 1, 31, 32, E // 2 + 7, E - 33, E - 1]
+    ref = run_chain_oracle(bq.cpu().numpy(), u[take].cpu().numpy(), wq[take].cpu().numpy())
+    mags = run_chain_oracle(bq.abs().cpu().numpy(), u[take].abs().cpu().numpy(), wq[take].cpu().numpy())
+    assert oracle.parity_error(v2[take].cpu().numpy(), ref, mags) <= TOL
+    assert lib().acro_b200_device_status() == _lib.OK
