@@ -11,6 +11,7 @@
 // Algorithmic HBM traffic per point: 8*DIM*DIM (X) [+ 8*DIM*DIM (Y != X)] + 8*DIM*DIM (D)
 // + 8 bytes per point-wise factor that varies with every point.
 #include "common.cuh"
+#include "tma.cuh"
 
 using namespace acro_b200_detail;
 
@@ -26,7 +27,9 @@ struct PointwiseArgs
     const double *X;
     const double *Y;
     double *D;
-    int64_t points;
+    int64_t points;        // points this launch covers
+    int64_t first_point;   // global number of its first point (X, Y, D already point at it)
+    int *wait_flag;
 };
 
 __device__ inline void copy_in(double *dst, const double *src, int count, bool vec)
@@ -49,7 +52,7 @@ __global__ void __launch_bounds__(kTile)
 pointwise_sym_kernel(const __grid_constant__ PointwiseArgs a)
 {
     constexpr int BLK = DIM * DIM;
-    extern __shared__ __align__(16) double smem[];
+    extern __shared__ __align__(128) double smem[];
     double *sx = smem;
     double *sy = SAME_XY ? smem : smem + kTile * BLK;
 
@@ -75,7 +78,7 @@ pointwise_sym_kernel(const __grid_constant__ PointwiseArgs a)
             if (a.d.n_scalars > 0)
             {
                 int64_t idx[ACRO_B200_MAX_POINT_LOOPS];
-                int64_t rest = p;
+                int64_t rest = a.first_point + p;
 #pragma unroll
                 for (int j = ACRO_B200_MAX_POINT_LOOPS - 1; j >= 0; --j)
                 {
@@ -142,9 +145,164 @@ pointwise_sym_kernel(const __grid_constant__ PointwiseArgs a)
     }
 }
 
-template <int DIM>
-int launch(const PointwiseArgs &args, cudaStream_t s)
+
+// Point-wise factor product s[p] for global point number gp (left to right, as the reference).
+__device__ __forceinline__ double scalar_product(const PointwiseArgs &a, int64_t gp)
 {
+    double s = 1.0;
+    int64_t idx[ACRO_B200_MAX_POINT_LOOPS];
+    int64_t rest = gp;
+#pragma unroll
+    for (int j = ACRO_B200_MAX_POINT_LOOPS - 1; j >= 0; --j)
+    {
+        if (j < a.d.n_point_loops)
+        {
+            idx[j] = rest % a.d.point_extent[j];
+            rest /= a.d.point_extent[j];
+        }
+        else idx[j] = 0;
+    }
+#pragma unroll
+    for (int i = 0; i < ACRO_B200_MAX_SCALARS; ++i)
+    {
+        if (i < a.d.n_scalars)
+        {
+            int64_t off = 0;
+#pragma unroll
+            for (int j = 0; j < ACRO_B200_MAX_POINT_LOOPS; ++j) off += idx[j] * a.d.scalar_step[i][j];
+            const double f = __ldg(a.scalar[i] + off);
+            s = (i == 0) ? f : __dmul_rn(s, f);
+        }
+    }
+    return s;
+}
+
+// Pipelined variant for "=": whole tiles travel by asynchronous bulk copies through a ring of
+// shared-memory buffers.  While the threads compute tile i in place, the loads of the next
+// tiles are in flight and the store of tile i-1 drains; one CTA barrier per tile.
+template <int DIM, bool SAME_XY, int STAGES>
+__global__ void __launch_bounds__(kTile)
+pointwise_sym_pipe_kernel(const __grid_constant__ PointwiseArgs a)
+{
+    constexpr int BLK = DIM * DIM;
+    constexpr int TILE = kTile * BLK;                 // doubles per tile buffer
+    constexpr uint32_t TILE_BYTES = TILE * 8;
+    extern __shared__ __align__(128) double smem[];
+    double *bx = smem;                                 // [STAGES][TILE]
+    double *by = smem + (SAME_XY ? 0 : STAGES * TILE);
+    __shared__ uint64_t full[STAGES];
+
+    const int64_t n_full = a.points / kTile;           // the ragged tail is a separate launch
+    const int tid = threadIdx.x;
+    if (tid == 0)
+    {
+        for (int i = 0; i < STAGES; ++i) mbar_init(&full[i], 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    auto load_tile = [&](int64_t tile, int st) {
+        mbar_arrive_expect_tx(&full[st], SAME_XY ? TILE_BYTES : 2 * TILE_BYTES);
+        bulk_load(bx + st * TILE, a.X + tile * TILE, TILE_BYTES, &full[st]);
+        if (!SAME_XY) bulk_load(by + st * TILE, a.Y + tile * TILE, TILE_BYTES, &full[st]);
+    };
+
+    if (tid == 0)
+    {
+        for (int j = 0; j < STAGES - 1; ++j)
+        {
+            const int64_t tile = blockIdx.x + static_cast<int64_t>(j) * gridDim.x;
+            if (tile < n_full) load_tile(tile, j);
+        }
+    }
+
+    int64_t i = 0;
+    for (int64_t tile = blockIdx.x; tile < n_full; tile += gridDim.x, ++i)
+    {
+        const int st = static_cast<int>(i % STAGES);
+        // the point-wise factors come straight from global memory: fetch them before waiting
+        const double s = a.d.n_scalars > 0 ? scalar_product(a, a.first_point + tile * kTile + tid) : 1.0;
+        if (!mbar_wait(&full[st], static_cast<uint32_t>((i / STAGES) & 1))) atomicExch(a.wait_flag, 1);
+
+        double *px = bx + st * TILE + tid * BLK;
+        const double *py = by + st * TILE + tid * BLK;
+        double x[BLK], y[BLK];
+#pragma unroll
+        for (int k = 0; k < BLK; ++k)
+        {
+            x[k] = px[k];
+            y[k] = SAME_XY ? x[k] : py[k];
+        }
+#pragma unroll
+        for (int m = 0; m < DIM; ++m)
+        {
+            double sxm[DIM];
+#pragma unroll
+            for (int l = 0; l < DIM; ++l) sxm[l] = (a.d.n_scalars > 0) ? __dmul_rn(s, x[m * DIM + l]) : x[m * DIM + l];
+#pragma unroll
+            for (int n = 0; n < DIM; ++n)
+            {
+                double acc = 0.0;
+#pragma unroll
+                for (int l = 0; l < DIM; ++l) acc = __dadd_rn(acc, __dmul_rn(sxm[l], y[n * DIM + l]));
+                px[m * DIM + n] = acc;
+            }
+        }
+        fence_proxy_async();     // the results must be visible to the bulk store
+        __syncthreads();
+        if (tid == 0)
+        {
+            bulk_store(a.D + tile * TILE, bx + st * TILE, TILE_BYTES);
+            bulk_commit();
+            // Refill the buffer tile i-1 used: its store is the second youngest group.
+            const int64_t next = tile + static_cast<int64_t>(STAGES - 1) * gridDim.x;
+            if (next < n_full)
+            {
+                bulk_wait_read<1>();
+                load_tile(next, static_cast<int>((i + STAGES - 1) % STAGES));
+            }
+        }
+    }
+    if (tid == 0) bulk_wait_all<0>();   // shared memory must outlive the stores that read it
+}
+
+template <int DIM, bool SAME_XY, int STAGES>
+int launch_pipe(const PointwiseArgs &args, cudaStream_t s, int ctas_per_sm)
+{
+    constexpr int BLK = DIM * DIM;
+    const size_t smem = static_cast<size_t>(STAGES) * kTile * BLK * sizeof(double) * (SAME_XY ? 1 : 2);
+    auto kernel = pointwise_sym_pipe_kernel<DIM, SAME_XY, STAGES>;
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_pointwise_sym (shared memory opt-in)");
+    const int64_t n_full = args.points / kTile;
+    int64_t grid = static_cast<int64_t>(sm_count()) * ctas_per_sm;
+    if (grid > n_full) grid = n_full;
+    kernel<<<static_cast<int>(grid), kTile, smem, s>>>(args);
+    return launch_status("acro_b200_pointwise_sym (pipelined)");
+}
+
+template <int DIM>
+int launch(const PointwiseArgs &args_in, cudaStream_t s)
+{
+    PointwiseArgs args = args_in;
+    // "=" on 16-byte aligned operands: whole tiles through the bulk-copy pipeline, then the
+    // ragged tail (if any) through the plain kernel below.
+    if (args.d.op == ACRO_B200_OP_ASSIGN && args.points >= kTile && aligned16(args.X) && aligned16(args.Y) && aligned16(args.D))
+    {
+        const bool same_xy = args.X == args.Y;
+        int rc;
+        if (DIM == 3) rc = same_xy ? launch_pipe<DIM, true, 4>(args, s, 3) : launch_pipe<DIM, false, 3>(args, s, 2);
+        else rc = same_xy ? launch_pipe<DIM, true, 4>(args, s, 4) : launch_pipe<DIM, false, 4>(args, s, 4);
+        if (rc != ACRO_B200_OK) return rc;
+        const int64_t done = (args.points / kTile) * kTile;
+        if (done == args.points) return ACRO_B200_OK;
+        constexpr int BLK2 = DIM * DIM;
+        args.X += done * BLK2;
+        args.Y += done * BLK2;
+        args.D += done * BLK2;
+        args.first_point += done;
+        args.points -= done;
+    }
     constexpr int BLK = DIM * DIM;
     const bool same = args.X == args.Y;
     const size_t smem = static_cast<size_t>(kTile) * BLK * sizeof(double) * (same ? 1 : 2);
@@ -187,6 +345,9 @@ int acro_b200_pointwise_sym(const acro_b200_pointwise_desc *desc, const double *
     args.D = D;
     args.points = 1;
     for (int j = 0; j < desc->n_point_loops; ++j) args.points *= desc->point_extent[j];
+    args.first_point = 0;
+    args.wait_flag = wait_flag_device_ptr();
+    if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_pointwise_sym (status flag)");
     for (int i = 0; i < ACRO_B200_MAX_SCALARS; ++i)
     {
         args.scalar[i] = nullptr;
