@@ -11,6 +11,14 @@
 // time (16 accumulator tiles), then routes each 8 x 32 block through a small per-warp
 // staging area so that rows leave as contiguous 256-byte stores.
 //
+// When B1 and B2 are the same matrix, M_e is symmetric: a second kernel (further down)
+// computes only the ni*(ni+1)/2 columns with i <= j and writes every off-diagonal entry
+// twice, at (i,j) and (j,i), which halves the tensor-core work (the two products
+// (W*B_i)*B_j and (W*B_j)*B_i differ only in rounding, well inside the tolerance).
+// Measured on B200, E = 2^18, 27 x 27: general kernel 0.926 ms; symmetric columns with the
+// mirrored entries stored straight to global memory 1.18 ms (scattered 8-byte stores);
+// symmetric columns through a shared-memory image and one bulk store 0.583 ms.
+//
 // Algorithmic HBM traffic per element: 8*64 (W) + 8*NI*NJ (M) bytes.
 #include "common.cuh"
 #include "dmma.cuh"
@@ -66,6 +74,8 @@ __device__ __forceinline__ void issue_w_load(Smem &s, const Rank1Args &a, int64_
     }
 }
 
+// NTG: 8-column tiles per column group of a warp.
+template <int NTG>
 __global__ void __launch_bounds__(NTHREADS, 2)
 rank1_gemm_kernel(const Rank1Args a)
 {
@@ -75,7 +85,9 @@ rank1_gemm_kernel(const Rank1Args a)
     const int warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int ni = a.ni, nj = a.nj, nc = ni * nj;
-    const int n_groups = (nc + 31) / 32;
+    const int n_cols = nc;
+    constexpr int GW = NTG * 8;                            // columns per group
+    const int n_groups = (n_cols + GW - 1) / GW;
     const int64_t n_tiles = (a.elements + ET - 1) / ET;
 
     if (tid == 0)
@@ -114,49 +126,50 @@ rank1_gemm_kernel(const Rank1Args a)
 
         for (int grp = warp; grp < n_groups; grp += WARPS)
         {
-            const int c0 = grp * 32;
-            // column -> (i, j) of this lane's B-fragment column in each of the 4 column tiles
-            int off1[4], off2[4];
+            const int c0 = grp * GW;
+            // column -> (i, j) of this lane's B-fragment column in each column tile
+            int off1[NTG], off2[NTG];
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
+            for (int nt = 0; nt < NTG; ++nt)
             {
                 int c = c0 + nt * 8 + g;
-                c = c < nc ? c : nc - 1;          // padded columns compute a copy that is never stored
+                c = c < n_cols ? c : n_cols - 1;   // padded columns compute a copy that is never stored
                 off1[nt] = c / nj;
                 off2[nt] = c - off1[nt] * nj;
             }
-            double acc[4][4][2];
+            double acc[4][NTG][2];
 #pragma unroll
             for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
+                for (int nt = 0; nt < NTG; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
 
 #pragma unroll 2
             for (int k0 = 0; k0 < QN; k0 += 4)
             {
-                double af[4], bf[4];
+                double af[4], bf[NTG];
 #pragma unroll
                 for (int mt = 0; mt < 4; ++mt) af[mt] = sw[(mt * 8 + g) * LDW + k0 + t];
                 const double *b1 = s.B1 + (k0 + t) * ni;
                 const double *b2 = s.B2 + (k0 + t) * nj;
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) bf[nt] = b1[off1[nt]] * b2[off2[nt]];
+                for (int nt = 0; nt < NTG; ++nt) bf[nt] = b1[off1[nt]] * b2[off2[nt]];
 #pragma unroll
                 for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
-                    for (int nt = 0; nt < 4; ++nt) dmma_m8n8k4(acc[mt][nt], af[mt], bf[nt]);
+                    for (int nt = 0; nt < NTG; ++nt) dmma_m8n8k4(acc[mt][nt], af[mt], bf[nt]);
             }
 
-            // epilogue: 8 x 32 blocks through the warp's staging rows, then contiguous row stores
+            // epilogue: 8 x GW blocks through the warp's staging rows, then contiguous row stores
             const int col = c0 + lane;
+            const int pos = col;
 #pragma unroll
             for (int mt = 0; mt < 4; ++mt)
             {
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt)
+                for (int nt = 0; nt < NTG; ++nt)
                     *reinterpret_cast<double2 *>(stg + g * LDS_STAGE + nt * 8 + 2 * t) = make_double2(acc[mt][nt][0], acc[mt][nt][1]);
                 __syncwarp();
-                if (col < nc)
+                if (lane < GW && col < n_cols)
                 {
 #pragma unroll
                     for (int r = 0; r < 8; ++r)
@@ -164,11 +177,12 @@ rank1_gemm_kernel(const Rank1Args a)
                         const int el = mt * 8 + r;
                         if (el < n_e)
                         {
-                            double *dst = a.M + (e0 + el) * nc + col;
-                            double v = stg[r * LDS_STAGE + lane];
-                            if (a.op == ACRO_B200_OP_ADD) v += *dst;
-                            else if (a.op == ACRO_B200_OP_SUB) v = *dst - v;
-                            __stcs(dst, v);
+                            double *row = a.M + (e0 + el) * nc;
+                            const double v = stg[r * LDS_STAGE + lane];
+                            double v1 = v;
+                            if (a.op == ACRO_B200_OP_ADD) v1 = row[pos] + v;
+                            else if (a.op == ACRO_B200_OP_SUB) v1 = row[pos] - v;
+                            __stcs(row + pos, v1);
                         }
                     }
                 }
@@ -181,6 +195,191 @@ rank1_gemm_kernel(const Rank1Args a)
 }
 
 }
+
+// ------------------------------------------------------------------ symmetric variant
+// B1 == B2: only the packed columns (i <= j) are computed.  16 warps share one 32-element
+// tile; warp w owns column tiles 3w..3w+2 for all four 8-element row tiles (24 accumulator
+// tiles).  Results are scattered, entry (i,j) and its mirror (j,i), into a shared-memory
+// image of 8 full element matrices, which then leaves as ONE contiguous bulk store; two
+// such images alternate so the store of one row tile drains while the next is scattered.
+constexpr int SYM_THREADS = 512;
+constexpr int SYM_NTW = 3;                                  // column tiles per warp
+constexpr int SYM_MAX_COLS = (SYM_THREADS / 32) * SYM_NTW * 8;   // 384 packed columns
+
+struct SymLayout
+{
+    int b_off, stage_off, stage_bytes, bar_off, total;     // byte offsets into dynamic shared memory
+};
+
+__host__ __device__ inline SymLayout sym_layout(int ni)
+{
+    SymLayout l;
+    const int w_bytes = 2 * ET * LDW * 8;
+    l.b_off = w_bytes;
+    const int b_bytes = ((QN * ni * 8 + 127) / 128) * 128;
+    l.stage_off = l.b_off + b_bytes;
+    l.stage_bytes = ((8 * ni * ni * 8 + 127) / 128) * 128;
+    l.bar_off = l.stage_off + 2 * l.stage_bytes;
+    l.total = l.bar_off + 64;
+    return l;
+}
+
+__global__ void __launch_bounds__(SYM_THREADS, 1)
+rank1_gemm_sym_kernel(const Rank1Args a)
+{
+    extern __shared__ __align__(128) unsigned char raw[];
+    const int ni = a.ni, nc = ni * ni, n_cols = ni * (ni + 1) / 2;
+    const SymLayout L = sym_layout(ni);
+    double *sW = reinterpret_cast<double *>(raw);                        // [2][ET * LDW]
+    double *sB = reinterpret_cast<double *>(raw + L.b_off);             // [QN][ni]
+    double *sStage0 = reinterpret_cast<double *>(raw + L.stage_off);    // [8][nc], twice
+    double *sStage1 = reinterpret_cast<double *>(raw + L.stage_off + L.stage_bytes);
+    uint64_t *full = reinterpret_cast<uint64_t *>(raw + L.bar_off);     // [2]
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t n_tiles = (a.elements + ET - 1) / ET;
+
+    if (tid == 0)
+    {
+        mbar_init(&full[0], 1);
+        mbar_init(&full[1], 1);
+        fence_mbar_init();
+    }
+    for (int i = tid; i < QN * ni; i += SYM_THREADS) sB[i] = a.B1[i];
+    __syncthreads();
+
+    // packed column c -> (i, j), row-major upper triangle; fixed per thread for the whole kernel
+    auto unpack = [&](int c, int &i, int &j) {
+        int row = 0, start = 0;
+        while (start + (ni - row) <= c) { start += ni - row; ++row; }
+        i = row;
+        j = row + (c - start);
+    };
+    int off1[SYM_NTW], off2[SYM_NTW];           // B-fragment column of this lane
+    int pos_d[SYM_NTW][2], pos_m[SYM_NTW][2];   // where this lane's two C-fragment columns go
+#pragma unroll
+    for (int nt = 0; nt < SYM_NTW; ++nt)
+    {
+        const int cbase = (warp * SYM_NTW + nt) * 8;
+        int c = cbase + g;
+        c = c < n_cols ? c : n_cols - 1;        // padded columns compute a copy that is never stored
+        unpack(c, off1[nt], off2[nt]);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+        {
+            const int cc = cbase + 2 * t + h;
+            pos_d[nt][h] = pos_m[nt][h] = -1;
+            if (cc < n_cols)
+            {
+                int i, j;
+                unpack(cc, i, j);
+                pos_d[nt][h] = i * ni + j;
+                if (i != j) pos_m[nt][h] = j * ni + i;
+            }
+        }
+    }
+
+    auto issue_w = [&](int64_t tile, int buf) {
+        const int64_t e0 = tile * ET;
+        if (!a.use_bulk || e0 >= a.elements) return;
+        if (tid < 32)
+        {
+            const int64_t left = a.elements - e0;
+            const int n_e = left < ET ? static_cast<int>(left) : ET;
+            if (tid == 0) mbar_arrive_expect_tx(&full[buf], n_e * QN * 8);
+            __syncwarp();
+            if (tid < n_e) bulk_load(sW + buf * ET * LDW + tid * LDW, a.W + (e0 + tid) * QN, QN * 8, &full[buf]);
+        }
+    };
+
+    int64_t tile = blockIdx.x;
+    issue_w(tile, 0);
+    uint32_t phase_bits = 0;
+    int buf = 0;
+    uint32_t images = 0;   // row-tile images written so far (selects the staging buffer)
+    const bool bulk_out = aligned16(a.M);
+
+    for (; tile < n_tiles; tile += gridDim.x)
+    {
+        issue_w(tile + gridDim.x, buf ^ 1);
+        const int64_t e0 = tile * ET;
+        const int64_t left = a.elements - e0;
+        const int n_e = left < ET ? static_cast<int>(left) : ET;
+        if (a.use_bulk)
+        {
+            if (!mbar_wait(&full[buf], (phase_bits >> buf) & 1u)) atomicExch(a.wait_flag, 1);
+            phase_bits ^= (1u << buf);
+        }
+        else
+        {
+            for (int i = tid; i < n_e * QN; i += SYM_THREADS) sW[buf * ET * LDW + (i / QN) * LDW + (i % QN)] = __ldcs(a.W + e0 * QN + i);
+            __syncthreads();
+        }
+        const double *sw = sW + buf * ET * LDW;
+
+        double acc[4][SYM_NTW][2];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < SYM_NTW; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
+#pragma unroll 2
+        for (int k0 = 0; k0 < QN; k0 += 4)
+        {
+            double af[4], bf[SYM_NTW];
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) af[mt] = sw[(mt * 8 + g) * LDW + k0 + t];
+            const double *b = sB + (k0 + t) * ni;
+#pragma unroll
+            for (int nt = 0; nt < SYM_NTW; ++nt) bf[nt] = b[off1[nt]] * b[off2[nt]];
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < SYM_NTW; ++nt) dmma_m8n8k4(acc[mt][nt], af[mt], bf[nt]);
+        }
+
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+        {
+            const int rows = n_e - mt * 8 < 8 ? (n_e - mt * 8 > 0 ? n_e - mt * 8 : 0) : 8;   // valid elements of this row tile
+            double *img = (images & 1u) ? sStage1 : sStage0;
+            // the image buffer was last stored two images ago: all but the newest store have drained
+            if (tid == 0 && images >= 2) bulk_wait_read<1>();
+            __syncthreads();
+            double *row = img + g * nc;
+#pragma unroll
+            for (int nt = 0; nt < SYM_NTW; ++nt)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                {
+                    if (pos_d[nt][h] >= 0) row[pos_d[nt][h]] = acc[mt][nt][h];
+                    if (pos_m[nt][h] >= 0) row[pos_m[nt][h]] = acc[mt][nt][h];
+                }
+            fence_proxy_async();
+            __syncthreads();
+            double *dst = a.M + (e0 + mt * 8) * nc;
+            const bool whole = bulk_out && rows == 8 && ((8 * nc) % 2 == 0);
+            if (whole)
+            {
+                if (tid == 0)
+                {
+                    bulk_store(dst, img, 8 * nc * 8);
+                    bulk_commit();
+                }
+            }
+            else
+            {
+                for (int i = tid; i < rows * nc; i += SYM_THREADS) __stcs(dst + i, img[i]);
+                if (tid == 0) bulk_commit();   // an empty group keeps the image/store numbering in step
+            }
+            ++images;
+        }
+        buf ^= 1;
+    }
+    if (tid == 0) bulk_wait_all<0>();   // shared memory must outlive the stores that read it
+}
+
 
 extern "C" {
 
@@ -212,12 +411,24 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
     args.use_bulk = aligned16(W) ? 1 : 0;
 
     const size_t smem = sizeof(Smem);
-    cudaError_t status = cudaFuncSetAttribute(rank1_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_rank1_gemm (shared memory opt-in)");
     const int64_t n_tiles = (elements + ET - 1) / ET;
+    const bool symmetric = (B1 == B2 && ni == nj && op == ACRO_B200_OP_ASSIGN && ni * (ni + 1) / 2 <= SYM_MAX_COLS);
+    if (symmetric)
+    {
+        const SymLayout L = sym_layout(ni);
+        cudaError_t st = cudaFuncSetAttribute(rank1_gemm_sym_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        if (st != cudaSuccess) return fail_cuda(st, "acro_b200_rank1_gemm (shared memory opt-in)");
+        int64_t g1 = sms;
+        if (g1 > n_tiles) g1 = n_tiles;
+        rank1_gemm_sym_kernel<<<static_cast<int>(g1), SYM_THREADS, L.total, as_stream(stream)>>>(args);
+        return launch_status("acro_b200_rank1_gemm (symmetric)");
+    }
+    auto kernel = rank1_gemm_kernel<4>;
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_rank1_gemm (shared memory opt-in)");
     int64_t grid = static_cast<int64_t>(sms) * 2;
     if (grid > n_tiles) grid = n_tiles;
-    rank1_gemm_kernel<<<static_cast<int>(grid), NTHREADS, smem, as_stream(stream)>>>(args);
+    kernel<<<static_cast<int>(grid), NTHREADS, smem, as_stream(stream)>>>(args);
     return launch_status("acro_b200_rank1_gemm");
 }
 

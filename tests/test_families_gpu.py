@@ -39,13 +39,16 @@ def status_ok():
 
 @pytest.mark.parametrize("elements,ni,nj,op,offset", [
     (32, 27, 27, 0, 0), (33, 27, 27, 0, 0), (1, 27, 27, 0, 0), (100, 27, 27, 1, 0), (257, 27, 27, 2, 0),
-    (64, 5, 7, 0, 0), (95, 32, 32, 0, 0), (70, 27, 27, 0, 1), (10000, 27, 27, 0, 0),
+    (64, 5, 7, 0, 0), (95, 32, 32, 0, 0), (70, 27, 27, 0, 1), (10000, 27, 27, 0, 0), (40, 27, 27, 0, 2), (75, 1, 1, 0, 0),
+    (50, 2, 2, 1, 0),
 ])
 def test_rank1_gemm_kernel(torch, elements, ni, nj, op, offset):
     rng = np.random.default_rng(elements + ni)
     w = rng.random((elements, 64)) + 0.5
     b1 = rng.random((64, ni)) * 2 - 1
-    b2 = b1 if ni == nj else rng.random((64, nj)) * 2 - 1
+    # the same matrix twice selects the symmetric path; offset == 2 forces two distinct square matrices
+    b2 = b1 if (ni == nj and offset != 2) else rng.random((64, nj)) * 2 - 1
+    offset = offset % 2
     m0 = rng.random((elements, ni, nj))
     prod, mags = np.zeros_like(m0), np.zeros_like(m0)
     oracle.contract("port", "M_e_i_j = W_e_q B_q_i C_q_j", prod, w, b1, b2)
