@@ -12,7 +12,8 @@
 // i3, i2, i1, k1, k2 entirely in its registers (U is read from shared memory, the Q threads
 // of an element reading the same address in the same instruction: a broadcast).  Stage 6
 // contracts k3, which crosses the plane owners: Y2 goes through shared memory and thread
-// (e, i1) finishes V_e_i1_*_*.  Tiles of 32 elements; U and W tiles arrive by asynchronous
+// (e, i1) finishes V_e_i1_*_* and writes it over its own Y2 slots (read into registers
+// first), so V needs no buffer of its own and three CTAs fit on an SM.  Tiles of 32 elements; U and W tiles arrive by asynchronous
 // bulk copies (per element for U, into slots padded to 66 doubles so that the elements of a
 // warp fall into different banks; one span for W), issued as soon as the previous tile's
 // copies are dead, so they overlap the rest of that tile and the other CTA of the SM.
@@ -32,14 +33,13 @@ constexpr int U_ELEM = P * P * P;         // 64
 constexpr int W_ELEM = Q * Q * Q;         // 125
 constexpr int U_STRIDE = U_ELEM + 2;      // padded slot, 16-byte multiple
 constexpr int Y_STRIDE = P * P * Q + 5;   // 85: conflict-free for both access patterns
-constexpr int V_ROW = P * P + 2;          // 18 doubles per (element, i1) row
+constexpr int Y_ROW = P * Q;              // 20 doubles per (element, i1) row of Y2; V reuses the first 16
 
 struct Smem
 {
     double U[ET * U_STRIDE];
     double W[ET * W_ELEM];
     double Y[ET * Y_STRIDE];
-    double V[ET * P * V_ROW];
     double B[Q * P];
     uint64_t bar;
 };
@@ -69,7 +69,7 @@ __device__ __forceinline__ void issue_tile_load(Smem &s, const MassArgs &a, int6
     }
 }
 
-__global__ void __launch_bounds__(NT, 2)
+__global__ void __launch_bounds__(NT, 3)
 sumfact_mass_kernel(const MassArgs a)
 {
     extern __shared__ __align__(128) unsigned char raw[];
@@ -195,44 +195,34 @@ sumfact_mass_kernel(const MassArgs a)
 
         if (ec < n_e && tid < ET * P)
         {
-            // stage 6: V_i1_i2_i3 = sum_k3 B_k3_i3 Y2_i1_i2_k3
-            const double *y = s.Y + ec * Y_STRIDE + i1c * P * Q;
-            double *v = s.V + (ec * P + i1c) * V_ROW;
+            // stage 6: V_i1_i2_i3 = sum_k3 B_k3_i3 Y2_i1_i2_k3, written over this thread's own Y2 row
+            double *y = s.Y + ec * Y_STRIDE + i1c * Y_ROW;
+            double yv[P][Q];
 #pragma unroll
             for (int i2 = 0; i2 < P; ++i2)
-            {
-                double yv[Q];
 #pragma unroll
-                for (int k = 0; k < Q; ++k) yv[k] = y[i2 * Q + k];
+                for (int k = 0; k < Q; ++k) yv[i2][k] = y[i2 * Q + k];
+#pragma unroll
+            for (int i2 = 0; i2 < P; ++i2)
 #pragma unroll
                 for (int i3 = 0; i3 < P; ++i3)
                 {
-                    double acc = Bm[0][i3] * yv[0];
+                    double acc = Bm[0][i3] * yv[i2][0];
 #pragma unroll
-                    for (int k = 1; k < Q; ++k) acc = fma(Bm[k][i3], yv[k], acc);
-                    v[i2 * P + i3] = acc;
+                    for (int k = 1; k < Q; ++k) acc = fma(Bm[k][i3], yv[i2][k], acc);
+                    y[i2 * P + i3] = acc;
                 }
-            }
         }
-        __syncthreads();   // V tile complete
+        __syncthreads();   // V tile complete (inside the Y buffer)
 
-        // contiguous coalesced store of the V tile (rows of 16 doubles, padded to 18 in shared memory)
+        // contiguous coalesced store of the V tile: entry i of element e sits at e*85 + (i/16)*20 + i%16
         double *dst = a.V + e0 * U_ELEM;
-        if (aligned16(a.V))
+        for (int i = tid; i < n_e * U_ELEM; i += NT)
         {
-            for (int i2 = tid; i2 < n_e * U_ELEM / 2; i2 += NT)
-            {
-                const int i = 2 * i2;
-                const double2 val = *reinterpret_cast<const double2 *>(s.V + (i / (P * P)) * V_ROW + (i % (P * P)));
-                __stcs(reinterpret_cast<double2 *>(dst + i), val);
-            }
+            const int el = i / U_ELEM, r = i % U_ELEM;
+            __stcs(dst + i, s.Y[el * Y_STRIDE + (r / (P * P)) * Y_ROW + (r % (P * P))]);
         }
-        else
-        {
-            for (int i = tid; i < n_e * U_ELEM; i += NT) __stcs(dst + i, s.V[(i / (P * P)) * V_ROW + (i % (P * P))]);
-        }
-        // The next tile writes Y only after every thread passed the first barrier above and V
-        // only after the next first barrier, so no third barrier is needed here.
+        __syncthreads();   // the next tile's stage 5 overwrites the Y buffer
     }
 }
 
@@ -265,7 +255,7 @@ int acro_b200_sumfact_mass(const double *B, const double *U, const double *W, do
     cudaError_t status = cudaFuncSetAttribute(sumfact_mass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (status != cudaSuccess) return fail_cuda(status, "acro_b200_sumfact_mass (shared memory opt-in)");
     const int64_t n_tiles = (elements + ET - 1) / ET;
-    int64_t grid = static_cast<int64_t>(sms) * 2;
+    int64_t grid = static_cast<int64_t>(sms) * 3;
     if (grid > n_tiles) grid = n_tiles;
     sumfact_mass_kernel<<<static_cast<int>(grid), NT, smem, as_stream(stream)>>>(args);
     return launch_status("acro_b200_sumfact_mass");
