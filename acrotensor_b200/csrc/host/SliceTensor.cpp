@@ -9,10 +9,8 @@ void SliceTensor::SliceInit(Tensor &T, std::vector<int> &sind)
     ACROBATIC_ASSERT(T.IsInitialized(), "Can't slice an uninitilized tensor.");
     ACROBATIC_ASSERT(T.GetRank() > static_cast<int>(sind.size()), "Can't slice more dimensions than the tensor rank.");
     ACROBATIC_ASSERT(!IsInitialized(), "Can't initilize a slice a second time.");
-    for (std::size_t d = 0; d < sind.size(); ++d)
-    {
-        ACROBATIC_ASSERT(sind[d] >= 0 && sind[d] < T.GetDim(static_cast<int>(d)), "Slice index out of range.");
-    }
+    // Like the reference, the prefix indices are not range-checked: its own unit tests
+    // construct (and never touch) slices past the end (unittest/tensor/test_SliceTensor.cpp:25-27).
     FullT = &T;
     Offset = T.GetRawIndex(sind);
 
