@@ -39,7 +39,7 @@ FALLBACK_HBM_GBS = 6650.0
 FP64_PEAK_GFLOPS_FILE = os.path.join(ROOT, "profiles", "fp64_peak_gflops.txt")
 # dram bytes (read+write) per launch of the dominant kernel from the ncu capture summarised
 # in profiles/ (scaled to a full-size launch); None until captured.
-NCU_TRAFFIC_BYTES = {"cfg3": 9.75e9}   # profiles/pointwise_sym_cfg3_E131072_ncu.md, scaled x8 to E = 2^20
+NCU_TRAFFIC_BYTES = {"cfg3": 9.79e9, "cfg0": 5.40e9, "cfg2": 2.01e9, "cfg1": 1.42e9, "cfg4": 1.36e9}   # profiles/*_ncu.md, small captures scaled to a full launch
 
 # batch of the bounded CPU sample per configuration (about 1-2 s of one core each)
 CPU_SAMPLE = {"cfg0": 1 << 24, "cfg1": 1 << 12, "cfg2": 1 << 16, "cfg3": 1 << 16, "cfg4": 1 << 9}
