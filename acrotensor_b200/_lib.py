@@ -76,6 +76,20 @@ SIGNATURES = {
     "acro_b200_batched_gemm": (_I, [_P, _P, _P, _I64, _I, _I, _I, _I, _P]),
     "acro_b200_sumfact_mass_supported": (_I, [_I, _I]),
     "acro_b200_sumfact_mass": (_I, [_P, _P, _P, _P, _I64, _I, _I, _P]),
+    "acro_b200_batch_inv_det": (_I, [_P, _P, _P, _I64, _I, _P]),
+    "acro_b200_flat_scatter": (_I, [_P, _P, _P, _I64, _P]),
+    "acro_b200_flat_sum_gather": (_I, [_P, _P, _P, _P, _I64, _P]),
+    "acro_index_mapping_create": (_I, [_I, _I, ctypes.POINTER(_P)]),
+    "acro_index_mapping_destroy": (_I, [_P]),
+    "acro_index_mapping_data": (_P, [_P]),
+    "acro_index_mapping_compute_inverse": (_I, [_P]),
+    "acro_index_mapping_inverse": (_P, [_P]),
+    "acro_index_mapping_inverse_offsets": (_P, [_P]),
+    "acro_engine_batch_matrix_inverse": (_I, [_P, _P, _P]),
+    "acro_engine_batch_matrix_det": (_I, [_P, _P, _P]),
+    "acro_engine_batch_matrix_inv_det": (_I, [_P, _P, _P, _P]),
+    "acro_engine_flat_indexed_scatter": (_I, [_P, _P, _P, _P]),
+    "acro_engine_flat_indexed_sum_gather": (_I, [_P, _P, _P, _P]),
     "acro_tensor_create": (_I, [_I, ctypes.POINTER(_I), _P, _P, _I, ctypes.POINTER(_P)]),
     "acro_tensor_slice": (_I, [_P, _I, ctypes.POINTER(_I), ctypes.POINTER(_P)]),
     "acro_tensor_destroy": (_I, [_P]),

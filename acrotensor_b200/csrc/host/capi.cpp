@@ -22,6 +22,12 @@ struct acro_tensor
     std::unique_ptr<acro::Tensor> t;
 };
 
+struct acro_index_mapping
+{
+    acro::IndexMapping m;
+    acro_index_mapping(int domain, int range) : m(domain, range) {}
+};
+
 struct acro_engine
 {
     acro::TensorEngine te;
@@ -261,6 +267,80 @@ int acro_engine_set_stream(acro_engine *e, void *stream)
     return guarded([&] {
         if (e == nullptr) acro::throw_error("null engine handle");
         e->te.SetCudaStream(stream);
+    });
+}
+
+int acro_index_mapping_create(int domain_size, int range_size, acro_index_mapping **out)
+{
+    return guarded([&] {
+        if (out == nullptr || domain_size < 1 || range_size < 1) acro::throw_error("acro_index_mapping_create: bad arguments");
+        *out = new acro_index_mapping(domain_size, range_size);
+    });
+}
+
+int acro_index_mapping_destroy(acro_index_mapping *m)
+{
+    delete m;
+    return ACRO_B200_OK;
+}
+
+int *acro_index_mapping_data(acro_index_mapping *m) { return m ? m->m.GetMap().GetData() : nullptr; }
+
+int acro_index_mapping_compute_inverse(acro_index_mapping *m)
+{
+    return guarded([&] {
+        if (m == nullptr) acro::throw_error("null index mapping handle");
+        m->m.ComputeInverse();
+    });
+}
+
+const int *acro_index_mapping_inverse(acro_index_mapping *m)
+{
+    return (m && m->m.IsInverseComputed()) ? m->m.GetInvMap().GetData() : nullptr;
+}
+
+const int *acro_index_mapping_inverse_offsets(acro_index_mapping *m)
+{
+    return (m && m->m.IsInverseComputed()) ? m->m.GetInvMapOffsets().GetData() : nullptr;
+}
+
+int acro_engine_batch_matrix_inverse(acro_engine *e, acro_tensor *Ainv, acro_tensor *A)
+{
+    return guarded([&] {
+        if (e == nullptr || Ainv == nullptr || A == nullptr) acro::throw_error("acro_engine_batch_matrix_inverse: null handle");
+        e->te.BatchMatrixInverse(*Ainv->t, *A->t);
+    });
+}
+
+int acro_engine_batch_matrix_det(acro_engine *e, acro_tensor *Adet, acro_tensor *A)
+{
+    return guarded([&] {
+        if (e == nullptr || Adet == nullptr || A == nullptr) acro::throw_error("acro_engine_batch_matrix_det: null handle");
+        e->te.BatchMatrixDet(*Adet->t, *A->t);
+    });
+}
+
+int acro_engine_batch_matrix_inv_det(acro_engine *e, acro_tensor *Ainv, acro_tensor *Adet, acro_tensor *A)
+{
+    return guarded([&] {
+        if (e == nullptr || Ainv == nullptr || Adet == nullptr || A == nullptr) acro::throw_error("acro_engine_batch_matrix_inv_det: null handle");
+        e->te.BatchMatrixInvDet(*Ainv->t, *Adet->t, *A->t);
+    });
+}
+
+int acro_engine_flat_indexed_scatter(acro_engine *e, acro_tensor *Aout, acro_tensor *Ain, acro_index_mapping *m)
+{
+    return guarded([&] {
+        if (e == nullptr || Aout == nullptr || Ain == nullptr || m == nullptr) acro::throw_error("acro_engine_flat_indexed_scatter: null handle");
+        e->te.FlatIndexedScatter(*Aout->t, *Ain->t, m->m);
+    });
+}
+
+int acro_engine_flat_indexed_sum_gather(acro_engine *e, acro_tensor *Aout, acro_tensor *Ain, acro_index_mapping *m)
+{
+    return guarded([&] {
+        if (e == nullptr || Aout == nullptr || Ain == nullptr || m == nullptr) acro::throw_error("acro_engine_flat_indexed_sum_gather: null handle");
+        e->te.FlatIndexedSumGather(*Aout->t, *Ain->t, m->m);
     });
 }
 

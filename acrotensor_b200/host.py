@@ -170,6 +170,46 @@ class SliceTensor(Tensor):
         super().__init__(_handle=h, _keep=parent)
 
 
+class IndexMapping:
+    """acro::IndexMapping(domain_size, range_size): ``M[i]`` in [0, domain_size) for i < range_size."""
+
+    def __init__(self, domain_size, range_size, values=None):
+        h = ctypes.c_void_p()
+        check(lib().acro_index_mapping_create(int(domain_size), int(range_size), ctypes.byref(h)))
+        self._h = h
+        self.domain_size, self.range_size = int(domain_size), int(range_size)
+        if values is not None:
+            self.numpy()[:] = values
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h is not None and _lib._lib is not None:
+            _lib._lib.acro_index_mapping_destroy(h)
+
+    def numpy(self):
+        """The host map as a writable int32 numpy view."""
+        buf = (ctypes.c_int * self.range_size).from_address(lib().acro_index_mapping_data(self._h))
+        return np.frombuffer(buf, dtype=np.int32)
+
+    def GetDomainSize(self):
+        return self.domain_size
+
+    def GetRangeSize(self):
+        return self.range_size
+
+    def ComputeInverse(self):
+        check(lib().acro_index_mapping_compute_inverse(self._h))
+
+    def inverse(self):
+        """(InvMap, InvMapOffsets) as numpy copies, or None before ComputeInverse."""
+        p, q = lib().acro_index_mapping_inverse(self._h), lib().acro_index_mapping_inverse_offsets(self._h)
+        if not p or not q:
+            return None
+        inv = np.frombuffer((ctypes.c_int * self.range_size).from_address(p), dtype=np.int32).copy()
+        off = np.frombuffer((ctypes.c_int * (self.domain_size + 1)).from_address(q), dtype=np.int32).copy()
+        return inv, off
+
+
 class TensorEngine:
     """acro::TensorEngine.  ``TE("S_i_j = A_n_i_j B_n", S, A, B)`` runs one contraction;
     Begin/EndMultiKernelLaunch record several and run them as one unit."""
@@ -213,6 +253,21 @@ class TensorEngine:
 
     def EndMultiKernelLaunchDescribe(self):
         return _text(lib().acro_engine_end_multi_describe, self._h)
+
+    def BatchMatrixInverse(self, Ainv, A):
+        check(lib().acro_engine_batch_matrix_inverse(self._h, Ainv._h, A._h))
+
+    def BatchMatrixDet(self, Adet, A):
+        check(lib().acro_engine_batch_matrix_det(self._h, Adet._h, A._h))
+
+    def BatchMatrixInvDet(self, Ainv, Adet, A):
+        check(lib().acro_engine_batch_matrix_inv_det(self._h, Ainv._h, Adet._h, A._h))
+
+    def FlatIndexedScatter(self, Aout, Ain, M):
+        check(lib().acro_engine_flat_indexed_scatter(self._h, Aout._h, Ain._h, M._h))
+
+    def FlatIndexedSumGather(self, Aout, Ain, M):
+        check(lib().acro_engine_flat_indexed_sum_gather(self._h, Aout._h, Ain._h, M._h))
 
     def Clear(self):
         check(lib().acro_engine_clear(self._h))

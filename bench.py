@@ -390,6 +390,46 @@ def spot_check(workloads, sessions, batches, world):
             "note": "cfg0 vs a device-side fp64 tree sum (relative); others vs the oracle on sampled units"}
 
 
+def run_ops(args):
+    """Side measurement (not part of the suite): the batched 3x3 inverse + determinant that
+    produces cfg 3's inputs, on [2^20, 64, 3, 3], device resident, through the engine API."""
+    import torch
+    import acrotensor_b200 as ab
+    torch.cuda.set_device(0)
+    E = max(1, int((1 << 20) * args.scale))
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    J = torch.rand((E, 64, 3, 3), generator=gen, device="cuda", dtype=torch.float64) * 0.4 - 0.2
+    for d in range(3):
+        J[..., d, d] += 1.0
+    inv, det = torch.empty_like(J), torch.empty((E, 64), device="cuda", dtype=torch.float64)
+    host = {n: torch.empty(t.shape, dtype=torch.float64).numpy() for n, t in (("J", J), ("inv", inv), ("det", det))}
+    TJ = ab.Tensor(J.shape, hdata=host["J"], ddata=J, ongpu=True)
+    TI = ab.Tensor(inv.shape, hdata=host["inv"], ddata=inv, ongpu=True)
+    TD = ab.Tensor(det.shape, hdata=host["det"], ddata=det, ongpu=True)
+    te = ab.TensorEngine("Cuda")
+    for _ in range(args.warmup):
+        te.BatchMatrixInvDet(TI, TD, TJ)
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        te.BatchMatrixInvDet(TI, TD, TJ)
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / args.steps
+    nbytes = E * 64 * (72 + 72 + 8)
+    hbm_peak, kind = measured_peaks()
+    ident = torch.einsum("ekij,eklj->ekil", J[:64], inv[:64])      # reference layout: inv holds the transposed inverse
+    err = float((ident - torch.eye(3, device="cuda", dtype=torch.float64)).abs().max())
+    print(json.dumps({"metric": "batch_inv_det_throughput", "value": round(nbytes / ms * 1e-6, 1), "unit": "GB/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "dtype": "f64",
+                      "config": {"workload": "BatchMatrixInvDet on [%d,64,3,3]" % E},
+                      "roofline": {"bound": "hbm", "achieved": round(nbytes / ms * 1e-6, 1), "peak": hbm_peak, "unit": "GB/s",
+                                   "frac": round(nbytes / ms * 1e-6 / hbm_peak, 4), "traffic": None},
+                      "identity_error": err}))
+
+
 # ----------------------------------------------------------------------------- CPU arms
 
 def cpu_time_workload(w, batch, threads, seed=0):
@@ -483,7 +523,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="suite", choices=["suite", "cfg0", "cfg1", "cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--workload", default="suite", choices=["suite", "cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "ops"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--scale", type=float, default=1.0, help="multiplies every batch size (debugging; 1.0 = benchmark sizes)")
     ap.add_argument("--seed", type=int, default=0)
@@ -492,7 +532,9 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
-    if args.impl == "reference":
+    if args.workload == "ops":
+        run_ops(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -4,4 +4,5 @@
 #include "TensorEngine.hpp"
 #include "Executor.hpp"
 #include "SliceTensor.hpp"
+#include "IndexMapping.hpp"
 #endif

@@ -20,6 +20,7 @@
 #include <vector>
 #include "DimensionedMultiKernel.hpp"
 #include "Executor.hpp"
+#include "IndexMapping.hpp"
 
 namespace acro
 {
@@ -72,6 +73,15 @@ class TensorEngine
     std::string GetImplementation(const char *bare_kernel_str, Tensor *out, std::vector<Tensor *> &inputs);
     std::string GetImplementation(std::string &kernel_str, Tensor *out, std::vector<Tensor *> &inputs);
 
+    // Non-contraction operations (kernel/TensorEngine.hpp:74-78 of the reference).
+    // The trailing two dimensions of A are a square matrix of extent <= 3; everything before is batch.
+    void BatchMatrixInverse(Tensor &Ainv, Tensor &A);
+    void BatchMatrixDet(Tensor &Adet, Tensor &A);
+    void BatchMatrixInvDet(Tensor &Ainv, Tensor &Adet, Tensor &A);
+    // Aout[i] = Ain[M[i]]   /   Aout[M[i]] += Ain[i] (Aout zeroed first)
+    void FlatIndexedScatter(Tensor &Aout, Tensor &Ain, IndexMapping &M);
+    void FlatIndexedSumGather(Tensor &Aout, Tensor &Ain, IndexMapping &M);
+
     void Clear();
     bool IsGPUAvailable() { return isCudaReady(); }
 
@@ -88,6 +98,8 @@ class TensorEngine
     TensorKernel *GetAddTensorKernel(std::string &kernel_str);
     DimensionedKernel *GetAddDimensionedKernel(TensorKernel *kernel, Tensor *output, std::vector<Tensor *> &inputs);
     KernelExecutor *GetAddKernelExecutor();
+    void RequireCuda(const char *what);
+    void *Stream();
     void Record(std::string &kernel_str, Tensor *output, std::vector<Tensor *> &inputs);
 
     std::string ExecutorType;

@@ -191,10 +191,29 @@ int acro_b200_sumfact_mass_supported(int p, int q);
 int acro_b200_sumfact_mass(const double *B, const double *U, const double *W, double *V,
                            int64_t elements, int p, int q, void *stream);
 
+/*
+ * Batched inverse and/or determinant of `count` dense dim x dim matrices (dim = 1, 2, 3), each
+ * dim*dim contiguous doubles.  Ainv or Adet may be NULL (not both); Ainv may alias A.  Same
+ * formulas, operation by operation, as the reference's CPU ops (ops/NativeCPUOps.hpp:38-86):
+ * bit-identical results, including its 3x3 convention of storing entry (r,c) of the inverse
+ * at position (c,r).  Replaces the CudaInv.., CudaDet.. and CudaInvDet.. kernels (ops/CudaGPUOps.cpp:108-275).
+ */
+int acro_b200_batch_inv_det(const double *A, double *Ainv, double *Adet, int64_t count, int dim, void *stream);
+
+/* Aout[i] = Ain[map[i]], i < range_size.  Replaces CudaScatter (ops/CudaGPUOps.cpp:278-285). */
+int acro_b200_flat_scatter(double *Aout, const double *Ain, const int *map, int64_t range_size, void *stream);
+
+/* Aout[d] = sum over k in [inv_offsets[d], inv_offsets[d+1]) of Ain[inv_map[k]], d < domain_size:
+ * the inverse map in CSR form, summed in ascending position (the reference CPU order), no
+ * atomics.  Replaces CudaSumGather (ops/CudaGPUOps.cpp:288-302). */
+int acro_b200_flat_sum_gather(double *Aout, const double *Ain, const int *inv_map, const int *inv_offsets,
+                              int64_t domain_size, void *stream);
+
 /* ---------------------------------------------------------------- engine layer */
 
 typedef struct acro_tensor acro_tensor;   /* an acro::Tensor */
 typedef struct acro_engine acro_engine;   /* an acro::TensorEngine */
+typedef struct acro_index_mapping acro_index_mapping;   /* an acro::IndexMapping */
 
 /* Tensor(dims, hdata, ddata, ongpu), tensor/Tensor.hpp:19-42.  hdata NULL = library-owned host buffer. */
 int acro_tensor_create(int rank, const int *dims, double *hdata, double *ddata, int ongpu, acro_tensor **out);
@@ -239,6 +258,25 @@ int acro_engine_end_multi_describe(acro_engine *e, char *buf, size_t buf_len);
 int acro_engine_clear(acro_engine *e);
 /* cudaStream_t as void*; applies to later launches of this engine. */
 int acro_engine_set_stream(acro_engine *e, void *stream);
+/* IndexMapping(domain_size, range_size), tensor/IndexMapping.hpp:14-48.  acro_index_mapping_data
+ * returns the host array of range_size ints to fill with M[i] in [0, domain_size). */
+int acro_index_mapping_create(int domain_size, int range_size, acro_index_mapping **out);
+int acro_index_mapping_destroy(acro_index_mapping *m);
+int *acro_index_mapping_data(acro_index_mapping *m);
+int acro_index_mapping_compute_inverse(acro_index_mapping *m);
+/* Host arrays of the inverse (range_size and domain_size+1 ints); NULL before it is computed. */
+const int *acro_index_mapping_inverse(acro_index_mapping *m);
+const int *acro_index_mapping_inverse_offsets(acro_index_mapping *m);
+
+/* BatchMatrixInverse / BatchMatrixDet / BatchMatrixInvDet, kernel/TensorEngine.cpp:627-690: the
+ * last two dimensions of A are the (square, <= 3) matrix, the leading ones the batch. */
+int acro_engine_batch_matrix_inverse(acro_engine *e, acro_tensor *Ainv, acro_tensor *A);
+int acro_engine_batch_matrix_det(acro_engine *e, acro_tensor *Adet, acro_tensor *A);
+int acro_engine_batch_matrix_inv_det(acro_engine *e, acro_tensor *Ainv, acro_tensor *Adet, acro_tensor *A);
+/* FlatIndexedScatter / FlatIndexedSumGather, kernel/TensorEngine.cpp:693-716. */
+int acro_engine_flat_indexed_scatter(acro_engine *e, acro_tensor *Aout, acro_tensor *Ain, acro_index_mapping *m);
+int acro_engine_flat_indexed_sum_gather(acro_engine *e, acro_tensor *Aout, acro_tensor *Ain, acro_index_mapping *m);
+
 /* Library-wide stream used by tensor copies / fills and by engines without their own. */
 int acro_b200_set_stream(void *stream);
 

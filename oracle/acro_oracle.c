@@ -270,6 +270,62 @@ API int acro_oracle_run(int n_tensors, double *const *data, const int *ranks, co
     return rc;
 }
 
+/*
+ * Batched inverse / determinant of 1x1, 2x2, 3x3 matrices: ops/NativeCPUOps.hpp:38-86 and
+ * ops/NativeCPUOps.cpp:11-120, operation by operation.  ainv or adet may be NULL.  The
+ * reference's 3x3 formula stores entry (r,c) of the true inverse at position (c,r).
+ */
+API int acro_oracle_batch_inv_det(const double *a, double *ainv, double *adet, int64_t count, int dim)
+{
+    if (dim < 1 || dim > 3 || count < 1 || !a) return fail("bad arguments to batch_inv_det", NULL);
+    const int blk = dim * dim;
+    for (int64_t m = 0; m < count; ++m) {
+        double A[9], inv[9], det;
+        for (int i = 0; i < blk; ++i) A[i] = a[m * blk + i];
+        if (dim == 1) det = A[0];
+        else if (dim == 2) det = (A[0] * A[3] - A[1] * A[2]);
+        else det = (A[0] * A[4] * A[8] + A[1] * A[5] * A[6] + A[2] * A[3] * A[7]
+                    - A[6] * A[4] * A[2] - A[7] * A[5] * A[0] - A[8] * A[3] * A[1]);
+        if (adet) adet[m] = det;
+        if (!ainv) continue;
+        double invdet = 1.0 / det;
+        if (dim == 1) inv[0] = 1.0 / det;
+        else if (dim == 2) {
+            inv[0] = invdet * A[3];
+            inv[1] = -invdet * A[1];
+            inv[2] = -invdet * A[2];
+            inv[3] = invdet * A[0];
+        } else {
+            inv[0] = invdet * (A[4] * A[8] - A[5] * A[7]);
+            inv[1] = invdet * (A[5] * A[6] - A[3] * A[8]);
+            inv[2] = invdet * (A[3] * A[7] - A[4] * A[6]);
+            inv[3] = invdet * (A[2] * A[7] - A[1] * A[8]);
+            inv[4] = invdet * (A[0] * A[8] - A[2] * A[6]);
+            inv[5] = invdet * (A[1] * A[6] - A[0] * A[7]);
+            inv[6] = invdet * (A[1] * A[5] - A[2] * A[4]);
+            inv[7] = invdet * (A[2] * A[3] - A[0] * A[5]);
+            inv[8] = invdet * (A[0] * A[4] - A[1] * A[3]);
+        }
+        for (int i = 0; i < blk; ++i) ainv[m * blk + i] = inv[i];
+    }
+    return 0;
+}
+
+/* Aout[i] = Ain[M[i]]   (ops/NativeCPUOps.cpp:123-130) */
+API int acro_oracle_flat_scatter(double *aout, const double *ain, const int *map, int64_t range)
+{
+    for (int64_t i = 0; i < range; ++i) aout[i] = ain[map[i]];
+    return 0;
+}
+
+/* Aout = 0; Aout[M[i]] += Ain[i] in ascending i   (ops/NativeCPUOps.cpp:133-144) */
+API int acro_oracle_flat_sum_gather(double *aout, const double *ain, const int *map, int64_t domain, int64_t range)
+{
+    for (int64_t d = 0; d < domain; ++d) aout[d] = 0.0;
+    for (int64_t i = 0; i < range; ++i) aout[map[i]] += ain[i];
+    return 0;
+}
+
 /* Grammar check only: 0 when the string parses, -1 otherwise. */
 API int acro_oracle_parses(const char *kernel)
 {

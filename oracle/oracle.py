@@ -132,3 +132,54 @@ def parity_error(got, ref, ref_abs):
     num = np.abs(np.asarray(got, dtype=np.float64) - ref)
     den = np.where(ref_abs > 0, ref_abs, 1.0)
     return float(np.max(num / den)) if num.size else 0.0
+
+
+def batch_inv_det(kind, a, want_inv=True, want_det=True):
+    """Inverse and/or determinant of the trailing dim x dim matrices of ``a``.
+    Returns (ainv or None, adet or None)."""
+    lib = _lib(kind)[0]
+    a = np.ascontiguousarray(a, dtype=np.float64)
+    dim = a.shape[-1]
+    ainv = np.empty_like(a) if want_inv else None
+    adet = np.empty(a.shape[:-2] if a.ndim > 2 else (1,)) if want_det else None
+    pa = a.ctypes.data_as(ctypes.c_void_p)
+    pi = ainv.ctypes.data_as(ctypes.c_void_p) if want_inv else None
+    pd = adet.ctypes.data_as(ctypes.c_void_p) if want_det else None
+    if kind == "port":
+        lib.acro_oracle_batch_inv_det.restype = ctypes.c_int
+        rc = lib.acro_oracle_batch_inv_det(pa, pi, pd, ctypes.c_int64(a.size // (dim * dim)), dim)
+    else:
+        lib.acro_ref_batch_inv_det.restype = ctypes.c_int
+        dims = (ctypes.c_int * a.ndim)(*a.shape)
+        rc = lib.acro_ref_batch_inv_det(pa, pi, pd, a.ndim, dims)
+    if rc != 0:
+        raise RuntimeError(_lib(kind)[2]().decode())
+    return ainv, adet
+
+
+def flat_indexed(kind, ain, mapping, domain, gather, with_inverse=False):
+    """FlatIndexedScatter (gather=False: out[i] = in[M[i]]) or FlatIndexedSumGather
+    (gather=True: out[M[i]] += in[i]).  With the reference library, ``with_inverse`` also
+    returns its ComputeInverse() arrays."""
+    lib = _lib(kind)[0]
+    mapping = np.ascontiguousarray(mapping, dtype=np.int32)
+    ain = np.ascontiguousarray(ain, dtype=np.float64)
+    rng = mapping.size
+    out = np.empty(domain if gather else rng)
+    pm = mapping.ctypes.data_as(ctypes.c_void_p)
+    po, pi = out.ctypes.data_as(ctypes.c_void_p), ain.ctypes.data_as(ctypes.c_void_p)
+    if kind == "port":
+        if gather:
+            lib.acro_oracle_flat_sum_gather(po, pi, pm, ctypes.c_int64(domain), ctypes.c_int64(rng))
+        else:
+            lib.acro_oracle_flat_scatter(po, pi, pm, ctypes.c_int64(rng))
+        return out
+    inv = np.empty(rng, dtype=np.int32)
+    off = np.empty(domain + 1, dtype=np.int32)
+    lib.acro_ref_flat_indexed.restype = ctypes.c_int
+    rc = lib.acro_ref_flat_indexed(po, pi, pm, int(domain), int(rng), int(bool(gather)),
+                                   inv.ctypes.data_as(ctypes.c_void_p) if with_inverse else None,
+                                   off.ctypes.data_as(ctypes.c_void_p) if with_inverse else None)
+    if rc != 0:
+        raise RuntimeError(_lib(kind)[2]().decode())
+    return (out, inv, off) if with_inverse else out

@@ -154,6 +154,67 @@ SHIM_API int acro_ref_run_slabs(int n_tensors, double *const *data, const int *r
     return 0;
 }
 
+// Batched inverse / determinant through the reference's TensorEngine("CPUInterpreted")
+// (kernel/TensorEngine.cpp:627-690 -> ops/NativeCPUOps.cpp:11-120).  Ainv or Adet may be null.
+SHIM_API int acro_ref_batch_inv_det(double *A, double *Ainv, double *Adet, int rank, const int *dims)
+{
+    try
+    {
+        std::vector<int> d(dims, dims + rank), dd(dims, dims + (rank > 2 ? rank - 2 : 0));
+        acro::TensorEngine TE("CPUInterpreted");
+        acro::Tensor a(d, A);
+        if (Ainv && Adet)
+        {
+            acro::Tensor inv(d, Ainv), det(dd, Adet);
+            TE.BatchMatrixInvDet(inv, det, a);
+        }
+        else if (Ainv)
+        {
+            acro::Tensor inv(d, Ainv);
+            TE.BatchMatrixInverse(inv, a);
+        }
+        else
+        {
+            acro::Tensor det(dd, Adet);
+            TE.BatchMatrixDet(det, a);
+        }
+        return 0;
+    }
+    catch (const std::exception &e)
+    {
+        g_err = e.what();
+        return -1;
+    }
+}
+
+// FlatIndexedScatter (gather == 0) or FlatIndexedSumGather (gather != 0) through the
+// reference's CPU engine (kernel/TensorEngine.cpp:693-716 -> ops/NativeCPUOps.cpp:123-144).
+// When inv / inv_off are given they receive the reference's ComputeInverse() result.
+SHIM_API int acro_ref_flat_indexed(double *Aout, double *Ain, const int *map, int domain, int range, int gather, int *inv, int *inv_off)
+{
+    try
+    {
+        acro::TensorEngine TE("CPUInterpreted");
+        acro::IndexMapping M(domain, range);
+        for (int i = 0; i < range; ++i) M[i] = map[i];
+        acro::Tensor out(gather ? domain : range, Aout), in(gather ? range : domain, Ain);
+        if (gather) TE.FlatIndexedSumGather(out, in, M);
+        else TE.FlatIndexedScatter(out, in, M);
+        if (inv && inv_off)
+        {
+            if (!M.IsInverseComputed()) M.ComputeInverse();
+            for (int i = 0; i < range; ++i) inv[i] = M.GetInvMap()[i];
+            for (int i = 0; i <= domain; ++i) inv_off[i] = M.GetInvMapOffsets()[i];
+        }
+        return 0;
+    }
+    catch (const std::exception &e)
+    {
+        g_err = e.what();
+        return -1;
+    }
+}
+
 SHIM_API int acro_ref_hardware_threads() {
     unsigned n = std::thread::hardware_concurrency();
     return n ? (int)n : 1;

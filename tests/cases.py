@@ -83,3 +83,25 @@ def written(case):
 
 def as_oracle_program(case, names):
     return [(k, names.index(o), [names.index(i) for i in ins]) for k, o, ins in case[1]]
+
+
+# ---------------------------------------------------------------- non-contraction operations
+# (name, matrix dim, batch shape): batched inverse / determinant, as in
+# unittest/kernel/test_TensorEngine.cpp:594-706 of the reference
+OPS_INV_DET = [("invdet1", 1, (10,)), ("invdet2", 2, (10,)), ("invdet3", 3, (10,)), ("invdet3_batch2", 3, (4, 2)),
+               ("invdet3_ragged", 3, (7, 64)), ("invdet2_big", 2, (1031,))]
+# (name, domain size, range size): FlatIndexedScatter / FlatIndexedSumGather, :708-745
+OPS_INDEXED = [("indexed_6_8", 6, 8), ("indexed_100_1000", 100, 1000), ("indexed_sparse", 50, 20)]
+
+
+def make_matrices(name, dim, batch):
+    rng = np.random.default_rng([11, dim, sum(map(ord, name))])
+    a = rng.random(tuple(batch) + (dim, dim)) * 2.0 - 1.0
+    a += 2.0 * np.eye(dim)          # comfortably invertible
+    return a
+
+
+def make_indexed(name, domain, rng_size):
+    rng = np.random.default_rng([13, domain, rng_size])
+    mapping = rng.integers(0, domain, rng_size).astype(np.int32)
+    return mapping, rng.random(domain) * 2.0 - 1.0, rng.random(rng_size) * 2.0 - 1.0

@@ -33,6 +33,16 @@ def main():
         oracle.run("ref", [tensors[n] for n in names], cases.as_oracle_program(case, names), multi=case[3])
         for n in cases.written(case):
             blob["%s/out/%s" % (name, n)] = tensors[n]
+    for name, dim, batch in cases.OPS_INV_DET:
+        a = cases.make_matrices(name, dim, batch)
+        blob["%s/inputs_sha256" % name] = np.array(cases.digest({"A": a}))
+        inv, det = oracle.batch_inv_det("ref", a)
+        blob["%s/out/inv" % name], blob["%s/out/det" % name] = inv, det
+    for name, domain, rng_size in cases.OPS_INDEXED:
+        mapping, dom_vals, rng_vals = cases.make_indexed(name, domain, rng_size)
+        blob["%s/inputs_sha256" % name] = np.array(cases.digest({"M": mapping, "D": dom_vals, "R": rng_vals}))
+        blob["%s/out/scatter" % name] = oracle.flat_indexed("ref", dom_vals, mapping, domain, False)
+        blob["%s/out/gather" % name] = oracle.flat_indexed("ref", rng_vals, mapping, domain, True)
     path = os.path.join(HERE, "reference_outputs.npz")
     np.savez_compressed(path, **blob)
     print("wrote", path, os.path.getsize(path), "bytes,", len(cases.all_cases()), "cases")
