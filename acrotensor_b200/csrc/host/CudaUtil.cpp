@@ -10,7 +10,9 @@ namespace acro
 
 namespace
 {
-void *g_stream = nullptr;
+// Per host thread, so that one thread can copy results back on its own stream while
+// another uploads the next inputs.
+thread_local void *g_stream = nullptr;
 }
 
 bool isCudaReady()

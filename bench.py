@@ -268,16 +268,37 @@ def run_ours(args):
     # end to end: host buffers, copies inside the timed region
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
 
+    # A second host thread with its own stream copies each result back (MoveFromGPU) while
+    # the main thread already uploads the next configuration's inputs: PCIe is full duplex.
+    import concurrent.futures
+    copy_stream = torch.cuda.Stream(device=dev)
+    pool = concurrent.futures.ThreadPoolExecutor(max_workers=1)
+
+    def fetch_on_copy_stream(sess, ready):
+        torch.cuda.set_device(dev)
+        ab.set_stream(copy_stream.cuda_stream)          # per-thread setting
+        copy_stream.wait_event(ready)                   # the kernels that produce the result
+        sess.fetch()                                     # MoveFromGPU of the result (D2H), synchronous for this thread
+
+    # Largest result first, so that its download overlaps the largest remaining upload.
+    e2e_order = sorted(range(len(workloads)), key=lambda i: -sum(outs_dev[i][n].numel() for n in outs_dev[i]))
+
     def e2e_step():
-        for i, (w, sess) in enumerate(zip(workloads, sessions)):
+        pending = []
+        for i in e2e_order:
+            w, sess = workloads[i], sessions[i]
             for name in w.names("in"):
                 sess.t[name].SwitchFromGPU()          # the host copy is the fresh one again
             for name in w.names("out") + w.names("tmp"):
                 sess.t[name].SwitchFromGPU()
-            sess.run()                                  # implicit MoveToGPU of every input (H2D)
+            sess.run()                                  # implicit MoveToGPU of every input (H2D), then the kernels
             if w.batch_contracted and world > 1:
                 allreduce_partial(outs_dev[i][w.names("out")[0]])
-            sess.fetch()                                # MoveFromGPU of the result (D2H)
+            ready = torch.cuda.Event()
+            ready.record()
+            pending.append(pool.submit(fetch_on_copy_stream, sess, ready))
+        for f in pending:
+            f.result()
 
     if pin_host:
         e2e_step()
@@ -354,6 +375,7 @@ def run_ours(args):
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(workloads, args)
         print(json.dumps(line))
+    pool.shutdown()
     if world > 1:
         dist.destroy_process_group()
 

@@ -18,8 +18,10 @@ bool isCudaReady();
 // for the calling thread; later library calls run in it.
 void setCudaContext(void *cuda_context);
 
-// The stream every kernel launch and copy of the library is issued on
-// (a cudaStream_t passed as void*; nullptr = the legacy default stream).
+// The stream the calling host thread's launches and copies are issued on (a
+// cudaStream_t passed as void*; nullptr = the legacy default stream).  The setting is
+// per thread: a second thread with its own stream can, for example, copy results
+// back while the first one uploads the next inputs.
 void setCudaStream(void *cuda_stream);
 void *getCudaStream();
 

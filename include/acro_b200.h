@@ -277,7 +277,8 @@ int acro_engine_batch_matrix_inv_det(acro_engine *e, acro_tensor *Ainv, acro_ten
 int acro_engine_flat_indexed_scatter(acro_engine *e, acro_tensor *Aout, acro_tensor *Ain, acro_index_mapping *m);
 int acro_engine_flat_indexed_sum_gather(acro_engine *e, acro_tensor *Aout, acro_tensor *Ain, acro_index_mapping *m);
 
-/* Library-wide stream used by tensor copies / fills and by engines without their own. */
+/* Stream used by the calling host thread's tensor copies / fills and by engines without their
+ * own stream (per thread; NULL = legacy default stream). */
 int acro_b200_set_stream(void *stream);
 
 /* Host-only introspection (no device needed): a text dump of the parser's view of a
