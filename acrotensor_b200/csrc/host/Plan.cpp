@@ -117,7 +117,8 @@ Step plan_generic(DimensionedKernel &k, int ki)
     s.bytes = io_bytes(k);
     s.flops = outer_points * terms * k.GetNumInputVars();   // (n_in - 1) multiplies + 1 add per term
     std::ostringstream note;
-    note << "thread per output entry: " << outer_points << " entries x " << terms << " terms";
+    if (acro_b200_generic_uses_wide_kernel(&g)) note << "CTA per output entry (fixed-order tree sum): " << outer_points << " entries x " << terms << " terms";
+    else note << "thread per output entry: " << outer_points << " entries x " << terms << " terms";
     s.note = note.str();
     return s;
 }

@@ -12,69 +12,143 @@ struct InputPointers
     const double *p[ACRO_B200_MAX_INPUTS];
 };
 
-template <int N_IN>   // 0 = run-time input count
+// Left-to-right product of the inputs at their current offsets (no fused multiply-add).
+template <int N_IN>
+__device__ __forceinline__ double product_at(const InputPointers &ins, const int64_t *off, int n_in)
+{
+    double prod = ins.p[0][off[0]];
+#pragma unroll
+    for (int v = 1; v < ACRO_B200_MAX_INPUTS; ++v)
+    {
+        if (v < (N_IN > 0 ? N_IN : n_in)) prod = __dmul_rn(prod, ins.p[v][off[v]]);
+    }
+    return prod;
+}
+
+template <int N_IN>
+__device__ __forceinline__ void advance(int64_t *off, const acro_b200_generic_desc &d, int loop, int64_t times, int n_in)
+{
+#pragma unroll
+    for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v)
+    {
+        if (v < (N_IN > 0 ? N_IN : n_in)) off[v] += times * d.in_step[v][loop];
+    }
+}
+
+// N_IN: input count (0 = run time).  N_CONTR: contracted loops handled by plain nested loops
+// (0..3), or -1 for any depth through an odometer.  One thread per output entry.
+template <int N_IN, int N_CONTR>
 __global__ void __launch_bounds__(256)
 generic_contract_kernel(const __grid_constant__ acro_b200_generic_desc d, double *__restrict__ out,
                         const __grid_constant__ InputPointers ins, int64_t outer_points, int64_t terms)
 {
     const int n_in = N_IN > 0 ? N_IN : d.n_inputs;
     const int n_outer = d.n_outer;
-    const int n_contr = d.n_loops - d.n_outer;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const bool narrow = outer_points <= 0x7fffffffLL;     // 32-bit index arithmetic is much cheaper
 
     for (int64_t point = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; point < outer_points; point += stride)
     {
         // Unflatten the output entry (last outer loop fastest) into per-variable offsets.
         int64_t out_off = 0;
-        int64_t in_off[ACRO_B200_MAX_INPUTS];
+        int64_t off[ACRO_B200_MAX_INPUTS];
 #pragma unroll
-        for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v) in_off[v] = 0;
-        int64_t rest = point;
-        for (int l = n_outer - 1; l >= 0; --l)
+        for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v) off[v] = 0;
+        if (narrow)
         {
-            const int64_t ext = d.extent[l];
-            const int64_t idx = rest % ext;
-            rest /= ext;
-            out_off += idx * d.out_step[l];
-#pragma unroll
-            for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v)
+            uint32_t rest = static_cast<uint32_t>(point);
+            for (int l = n_outer - 1; l >= 0; --l)
             {
-                if (v < n_in) in_off[v] += idx * d.in_step[v][l];
+                const uint32_t ext = static_cast<uint32_t>(d.extent[l]);
+                const uint32_t q = rest / ext;
+                const int64_t idx = rest - q * ext;
+                rest = q;
+                out_off += idx * d.out_step[l];
+                advance<N_IN>(off, d, l, idx, n_in);
+            }
+        }
+        else
+        {
+            int64_t rest = point;
+            for (int l = n_outer - 1; l >= 0; --l)
+            {
+                const int64_t ext = d.extent[l];
+                const int64_t idx = rest % ext;
+                rest /= ext;
+                out_off += idx * d.out_step[l];
+                advance<N_IN>(off, d, l, idx, n_in);
             }
         }
 
         double acc = (d.op == ACRO_B200_OP_ADD) ? out[out_off] : 0.0;
-        int32_t counter[ACRO_B200_MAX_LOOPS];
-        for (int c = 0; c < n_contr; ++c) counter[c] = 0;
-
-        for (int64_t term = 0; term < terms; ++term)
+        if (N_CONTR == 0)
         {
-            double prod = ins.p[0][in_off[0]];
-#pragma unroll
-            for (int v = 1; v < ACRO_B200_MAX_INPUTS; ++v)
+            acc = __dadd_rn(acc, product_at<N_IN>(ins, off, n_in));
+        }
+        else if (N_CONTR == 1)
+        {
+            const int l0 = n_outer;
+            const int e0 = static_cast<int>(d.extent[l0]);
+            for (int i = 0; i < e0; ++i)
             {
-                if (v < n_in) prod = __dmul_rn(prod, ins.p[v][in_off[v]]);
+                acc = __dadd_rn(acc, product_at<N_IN>(ins, off, n_in));
+                advance<N_IN>(off, d, l0, 1, n_in);
             }
-            acc = __dadd_rn(acc, prod);
-
-            // Odometer over the contracted loops, innermost fastest.
-            for (int c = n_contr - 1; c >= 0; --c)
+        }
+        else if (N_CONTR == 2)
+        {
+            const int l0 = n_outer, l1 = n_outer + 1;
+            const int e0 = static_cast<int>(d.extent[l0]), e1 = static_cast<int>(d.extent[l1]);
+            for (int i = 0; i < e0; ++i)
             {
-                const int l = n_outer + c;
-                if (++counter[c] < d.extent[l])
+                for (int j = 0; j < e1; ++j)
                 {
-#pragma unroll
-                    for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v)
-                    {
-                        if (v < n_in) in_off[v] += d.in_step[v][l];
-                    }
-                    break;
+                    acc = __dadd_rn(acc, product_at<N_IN>(ins, off, n_in));
+                    advance<N_IN>(off, d, l1, 1, n_in);
                 }
-                counter[c] = 0;
-#pragma unroll
-                for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v)
+                advance<N_IN>(off, d, l1, -static_cast<int64_t>(e1), n_in);
+                advance<N_IN>(off, d, l0, 1, n_in);
+            }
+        }
+        else if (N_CONTR == 3)
+        {
+            const int l0 = n_outer, l1 = n_outer + 1, l2 = n_outer + 2;
+            const int e0 = static_cast<int>(d.extent[l0]), e1 = static_cast<int>(d.extent[l1]), e2 = static_cast<int>(d.extent[l2]);
+            for (int i = 0; i < e0; ++i)
+            {
+                for (int j = 0; j < e1; ++j)
                 {
-                    if (v < n_in) in_off[v] -= d.in_step[v][l] * (d.extent[l] - 1);
+                    for (int k = 0; k < e2; ++k)
+                    {
+                        acc = __dadd_rn(acc, product_at<N_IN>(ins, off, n_in));
+                        advance<N_IN>(off, d, l2, 1, n_in);
+                    }
+                    advance<N_IN>(off, d, l2, -static_cast<int64_t>(e2), n_in);
+                    advance<N_IN>(off, d, l1, 1, n_in);
+                }
+                advance<N_IN>(off, d, l1, -static_cast<int64_t>(e1), n_in);
+                advance<N_IN>(off, d, l0, 1, n_in);
+            }
+        }
+        else
+        {
+            // any depth: odometer over the contracted loops, innermost fastest
+            const int n_contr = d.n_loops - d.n_outer;
+            int32_t counter[ACRO_B200_MAX_LOOPS];
+            for (int c = 0; c < n_contr; ++c) counter[c] = 0;
+            for (int64_t term = 0; term < terms; ++term)
+            {
+                acc = __dadd_rn(acc, product_at<N_IN>(ins, off, n_in));
+                for (int c = n_contr - 1; c >= 0; --c)
+                {
+                    const int l = n_outer + c;
+                    if (++counter[c] < d.extent[l])
+                    {
+                        advance<N_IN>(off, d, l, 1, n_in);
+                        break;
+                    }
+                    counter[c] = 0;
+                    advance<N_IN>(off, d, l, -(d.extent[l] - 1), n_in);
                 }
             }
         }
@@ -84,6 +158,90 @@ generic_contract_kernel(const __grid_constant__ acro_b200_generic_desc d, double
     }
 }
 
+// Few output entries but a long contraction (for example "S_a = X_n_a Y_n_a"): one CTA per
+// output entry, the terms split over its threads and combined in a fixed order.  The sum
+// order differs from the reference's sequential one (results agree to rounding, and are
+// reproducible run to run); the one-thread-per-entry kernel above would leave the GPU idle.
+constexpr int kWideThreads = 256;
+
+template <int N_IN>
+__global__ void __launch_bounds__(kWideThreads)
+generic_wide_kernel(const __grid_constant__ acro_b200_generic_desc d, double *__restrict__ out,
+                    const __grid_constant__ InputPointers ins, int64_t outer_points, int64_t terms)
+{
+    __shared__ double partial[kWideThreads];
+    const int n_in = N_IN > 0 ? N_IN : d.n_inputs;
+    const int n_outer = d.n_outer, n_loops = d.n_loops;
+    for (int64_t point = blockIdx.x; point < outer_points; point += gridDim.x)
+    {
+        int64_t out_off = 0;
+        int64_t base[ACRO_B200_MAX_INPUTS];
+#pragma unroll
+        for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v) base[v] = 0;
+        int64_t rest = point;
+        for (int l = n_outer - 1; l >= 0; --l)
+        {
+            const int64_t idx = rest % d.extent[l];
+            rest /= d.extent[l];
+            out_off += idx * d.out_step[l];
+            advance<N_IN>(base, d, l, idx, n_in);
+        }
+        double acc = 0.0;
+        for (int64_t term = threadIdx.x; term < terms; term += kWideThreads)
+        {
+            int64_t off[ACRO_B200_MAX_INPUTS];
+#pragma unroll
+            for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v) off[v] = base[v];
+            int64_t r = term;
+            for (int l = n_loops - 1; l >= n_outer; --l)
+            {
+                const int64_t idx = r % d.extent[l];
+                r /= d.extent[l];
+                advance<N_IN>(off, d, l, idx, n_in);
+            }
+            acc = __dadd_rn(acc, product_at<N_IN>(ins, off, n_in));
+        }
+        partial[threadIdx.x] = acc;
+        __syncthreads();
+        for (int width = kWideThreads / 2; width > 0; width >>= 1)
+        {
+            if (threadIdx.x < width) partial[threadIdx.x] = __dadd_rn(partial[threadIdx.x], partial[threadIdx.x + width]);
+            __syncthreads();
+        }
+        if (threadIdx.x == 0)
+        {
+            const double total = partial[0];
+            if (d.op == ACRO_B200_OP_ASSIGN) out[out_off] = total;
+            else if (d.op == ACRO_B200_OP_ADD) out[out_off] = __dadd_rn(out[out_off], total);
+            else out[out_off] = __dsub_rn(out[out_off], total);
+        }
+        __syncthreads();
+    }
+}
+
+template <int N_IN>
+void launch_thread_per_entry(const acro_b200_generic_desc &d, double *out, const InputPointers &ins, int64_t outer_points,
+                             int64_t terms, int grid, cudaStream_t s)
+{
+    switch (d.n_loops - d.n_outer)
+    {
+        case 0: generic_contract_kernel<N_IN, 0><<<grid, 256, 0, s>>>(d, out, ins, outer_points, terms); break;
+        case 1: generic_contract_kernel<N_IN, 1><<<grid, 256, 0, s>>>(d, out, ins, outer_points, terms); break;
+        case 2: generic_contract_kernel<N_IN, 2><<<grid, 256, 0, s>>>(d, out, ins, outer_points, terms); break;
+        case 3: generic_contract_kernel<N_IN, 3><<<grid, 256, 0, s>>>(d, out, ins, outer_points, terms); break;
+        default: generic_contract_kernel<N_IN, -1><<<grid, 256, 0, s>>>(d, out, ins, outer_points, terms); break;
+    }
+}
+
+}
+
+// 1 when the launch would use the CTA-per-entry kernel: few output entries, long contraction.
+extern "C" int acro_b200_generic_uses_wide_kernel(const acro_b200_generic_desc *desc)
+{
+    if (desc == nullptr) return 0;
+    int64_t outer_points = 1, terms = 1;
+    for (int l = 0; l < desc->n_loops && l < ACRO_B200_MAX_LOOPS; ++l) (l < desc->n_outer ? outer_points : terms) *= desc->extent[l];
+    return (outer_points <= 2048 && terms >= 16384) ? 1 : 0;
 }
 
 extern "C" int acro_b200_generic_launch(const acro_b200_generic_desc *desc, double *out, const double *const *inputs, void *stream)
@@ -108,17 +266,31 @@ extern "C" int acro_b200_generic_launch(const acro_b200_generic_desc *desc, doub
     }
     if (sm_count() <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_generic_launch");
 
+    cudaStream_t s = as_stream(stream);
+    if (acro_b200_generic_uses_wide_kernel(desc))
+    {
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+        const int grid = static_cast<int>(outer_points < cap ? outer_points : cap);
+        switch (desc->n_inputs)
+        {
+            case 1: generic_wide_kernel<1><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, outer_points, terms); break;
+            case 2: generic_wide_kernel<2><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, outer_points, terms); break;
+            case 3: generic_wide_kernel<3><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, outer_points, terms); break;
+            default: generic_wide_kernel<0><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, outer_points, terms); break;
+        }
+        return launch_status("acro_b200_generic_launch (wide)");
+    }
     const int64_t blocks_needed = (outer_points + 255) / 256;
     const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
     const int grid = static_cast<int>(blocks_needed < cap ? blocks_needed : cap);
-    cudaStream_t s = as_stream(stream);
     switch (desc->n_inputs)
     {
-        case 1: generic_contract_kernel<1><<<grid, 256, 0, s>>>(*desc, out, ins, outer_points, terms); break;
-        case 2: generic_contract_kernel<2><<<grid, 256, 0, s>>>(*desc, out, ins, outer_points, terms); break;
-        case 3: generic_contract_kernel<3><<<grid, 256, 0, s>>>(*desc, out, ins, outer_points, terms); break;
-        case 4: generic_contract_kernel<4><<<grid, 256, 0, s>>>(*desc, out, ins, outer_points, terms); break;
-        default: generic_contract_kernel<0><<<grid, 256, 0, s>>>(*desc, out, ins, outer_points, terms); break;
+        case 1: launch_thread_per_entry<1>(*desc, out, ins, outer_points, terms, grid, s); break;
+        case 2: launch_thread_per_entry<2>(*desc, out, ins, outer_points, terms, grid, s); break;
+        case 3: launch_thread_per_entry<3>(*desc, out, ins, outer_points, terms, grid, s); break;
+        case 4: launch_thread_per_entry<4>(*desc, out, ins, outer_points, terms, grid, s); break;
+        case 5: launch_thread_per_entry<5>(*desc, out, ins, outer_points, terms, grid, s); break;
+        default: launch_thread_per_entry<0>(*desc, out, ins, outer_points, terms, grid, s); break;
     }
     return launch_status("acro_b200_generic_launch");
 }

@@ -194,52 +194,61 @@ rank1_gemm_kernel(const Rank1Args a)
     }
 }
 
-}
 
 // ------------------------------------------------------------------ symmetric variant
-// B1 == B2: only the packed columns (i <= j) are computed.  16 warps share one 32-element
-// tile; warp w owns column tiles 3w..3w+2 for all four 8-element row tiles (24 accumulator
-// tiles).  Results are scattered, entry (i,j) and its mirror (j,i), into a shared-memory
-// image of 8 full element matrices, which then leaves as ONE contiguous bulk store; two
-// such images alternate so the store of one row tile drains while the next is scattered.
-constexpr int SYM_THREADS = 512;
-constexpr int SYM_NTW = 3;                                  // column tiles per warp
-constexpr int SYM_MAX_COLS = (SYM_THREADS / 32) * SYM_NTW * 8;   // 384 packed columns
+// B1 == B2: only the packed columns (i <= j) are computed.  The warps of a CTA share one
+// tile of MT*8 elements; warp w owns column tiles NTW*w .. NTW*w+NTW-1 for all MT row tiles.
+// Results are scattered, entry (i,j) and its mirror (j,i), into a shared-memory image of 8
+// full element matrices, which then leaves as ONE contiguous bulk store; IMAGES such images
+// alternate so the store of one row tile drains while the next is scattered.
+// Measured on B200 (E = 2^18, 27 x 27): 16 warps x 3 column tiles x 4 row tiles, 2 images,
+// one CTA per SM: 0.583 ms; 8 warps x 6 x 2, 1 image, two CTAs per SM: 0.652 ms.
+template <int WARPS_, int NTW_, int MT_, int IMAGES_, int CTAS_>
+struct SymCfg
+{
+    static constexpr int WARPS = WARPS_, NTW = NTW_, MT = MT_, IMAGES = IMAGES_, CTAS = CTAS_;
+    static constexpr int THREADS = WARPS * 32;
+    static constexpr int TILE_E = MT * 8;                 // elements per tile
+    static constexpr int MAX_COLS = WARPS * NTW * 8;      // packed columns covered
+};
 
 struct SymLayout
 {
-    int b_off, stage_off, stage_bytes, bar_off, total;     // byte offsets into dynamic shared memory
+    int ldb, b_off, stage_off, stage_bytes, bar_off, total;     // byte offsets into dynamic shared memory
 };
 
-__host__ __device__ inline SymLayout sym_layout(int ni)
+__host__ __device__ inline SymLayout sym_layout(int ni, int tile_e, int images)
 {
     SymLayout l;
-    const int w_bytes = 2 * ET * LDW * 8;
+    l.ldb = ni;
+    while (l.ldb % 8 != 4) ++l.ldb;                        // row stride = 4 mod 8 doubles: conflict-free fragment loads
+    const int w_bytes = 2 * tile_e * LDW * 8;
     l.b_off = w_bytes;
-    const int b_bytes = ((QN * ni * 8 + 127) / 128) * 128;
+    const int b_bytes = ((QN * l.ldb * 8 + 127) / 128) * 128;
     l.stage_off = l.b_off + b_bytes;
     l.stage_bytes = ((8 * ni * ni * 8 + 127) / 128) * 128;
-    l.bar_off = l.stage_off + 2 * l.stage_bytes;
+    l.bar_off = l.stage_off + images * l.stage_bytes;
     l.total = l.bar_off + 64;
     return l;
 }
 
-__global__ void __launch_bounds__(SYM_THREADS, 1)
+template <class C>
+__global__ void __launch_bounds__(C::THREADS, C::CTAS)
 rank1_gemm_sym_kernel(const Rank1Args a)
 {
+    constexpr int NTW = C::NTW, MT = C::MT, TE = C::TILE_E, THREADS = C::THREADS;
     extern __shared__ __align__(128) unsigned char raw[];
     const int ni = a.ni, nc = ni * ni, n_cols = ni * (ni + 1) / 2;
-    const SymLayout L = sym_layout(ni);
-    double *sW = reinterpret_cast<double *>(raw);                        // [2][ET * LDW]
-    double *sB = reinterpret_cast<double *>(raw + L.b_off);             // [QN][ni]
-    double *sStage0 = reinterpret_cast<double *>(raw + L.stage_off);    // [8][nc], twice
-    double *sStage1 = reinterpret_cast<double *>(raw + L.stage_off + L.stage_bytes);
+    const SymLayout L = sym_layout(ni, TE, C::IMAGES);
+    const int ldb = L.ldb;
+    double *sW = reinterpret_cast<double *>(raw);                        // [2][TE * LDW]
+    double *sB = reinterpret_cast<double *>(raw + L.b_off);             // [QN][ldb]
     uint64_t *full = reinterpret_cast<uint64_t *>(raw + L.bar_off);     // [2]
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int64_t n_tiles = (a.elements + ET - 1) / ET;
+    const int64_t n_tiles = (a.elements + TE - 1) / TE;
 
     if (tid == 0)
     {
@@ -247,7 +256,7 @@ rank1_gemm_sym_kernel(const Rank1Args a)
         mbar_init(&full[1], 1);
         fence_mbar_init();
     }
-    for (int i = tid; i < QN * ni; i += SYM_THREADS) sB[i] = a.B1[i];
+    for (int i = tid; i < QN * ni; i += THREADS) sB[(i / ni) * ldb + (i % ni)] = a.B1[i];
     __syncthreads();
 
     // packed column c -> (i, j), row-major upper triangle; fixed per thread for the whole kernel
@@ -257,12 +266,12 @@ rank1_gemm_sym_kernel(const Rank1Args a)
         i = row;
         j = row + (c - start);
     };
-    int off1[SYM_NTW], off2[SYM_NTW];           // B-fragment column of this lane
-    int pos_d[SYM_NTW][2], pos_m[SYM_NTW][2];   // where this lane's two C-fragment columns go
+    int off1[NTW], off2[NTW];    // B-fragment column of this lane
+    int pos_d[NTW][2];           // where this lane's two C-fragment columns go (-1: padding)
 #pragma unroll
-    for (int nt = 0; nt < SYM_NTW; ++nt)
+    for (int nt = 0; nt < NTW; ++nt)
     {
-        const int cbase = (warp * SYM_NTW + nt) * 8;
+        const int cbase = (warp * NTW + nt) * 8;
         int c = cbase + g;
         c = c < n_cols ? c : n_cols - 1;        // padded columns compute a copy that is never stored
         unpack(c, off1[nt], off2[nt]);
@@ -270,27 +279,26 @@ rank1_gemm_sym_kernel(const Rank1Args a)
         for (int h = 0; h < 2; ++h)
         {
             const int cc = cbase + 2 * t + h;
-            pos_d[nt][h] = pos_m[nt][h] = -1;
+            pos_d[nt][h] = -1;
             if (cc < n_cols)
             {
                 int i, j;
                 unpack(cc, i, j);
                 pos_d[nt][h] = i * ni + j;
-                if (i != j) pos_m[nt][h] = j * ni + i;
             }
         }
     }
 
     auto issue_w = [&](int64_t tile, int buf) {
-        const int64_t e0 = tile * ET;
+        const int64_t e0 = tile * TE;
         if (!a.use_bulk || e0 >= a.elements) return;
         if (tid < 32)
         {
             const int64_t left = a.elements - e0;
-            const int n_e = left < ET ? static_cast<int>(left) : ET;
+            const int n_e = left < TE ? static_cast<int>(left) : TE;
             if (tid == 0) mbar_arrive_expect_tx(&full[buf], n_e * QN * 8);
             __syncwarp();
-            if (tid < n_e) bulk_load(sW + buf * ET * LDW + tid * LDW, a.W + (e0 + tid) * QN, QN * 8, &full[buf]);
+            if (tid < n_e) bulk_load(sW + buf * TE * LDW + tid * LDW, a.W + (e0 + tid) * QN, QN * 8, &full[buf]);
         }
     };
 
@@ -304,9 +312,9 @@ rank1_gemm_sym_kernel(const Rank1Args a)
     for (; tile < n_tiles; tile += gridDim.x)
     {
         issue_w(tile + gridDim.x, buf ^ 1);
-        const int64_t e0 = tile * ET;
+        const int64_t e0 = tile * TE;
         const int64_t left = a.elements - e0;
-        const int n_e = left < ET ? static_cast<int>(left) : ET;
+        const int n_e = left < TE ? static_cast<int>(left) : TE;
         if (a.use_bulk)
         {
             if (!mbar_wait(&full[buf], (phase_bits >> buf) & 1u)) atomicExch(a.wait_flag, 1);
@@ -314,53 +322,57 @@ rank1_gemm_sym_kernel(const Rank1Args a)
         }
         else
         {
-            for (int i = tid; i < n_e * QN; i += SYM_THREADS) sW[buf * ET * LDW + (i / QN) * LDW + (i % QN)] = __ldcs(a.W + e0 * QN + i);
+            for (int i = tid; i < n_e * QN; i += THREADS) sW[buf * TE * LDW + (i / QN) * LDW + (i % QN)] = __ldcs(a.W + e0 * QN + i);
             __syncthreads();
         }
-        const double *sw = sW + buf * ET * LDW;
+        const double *sw = sW + buf * TE * LDW;
 
-        double acc[4][SYM_NTW][2];
+        double acc[MT][NTW][2];
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt)
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int nt = 0; nt < SYM_NTW; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
+            for (int nt = 0; nt < NTW; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
 #pragma unroll 2
         for (int k0 = 0; k0 < QN; k0 += 4)
         {
-            double af[4], bf[SYM_NTW];
+            double af[MT], bf[NTW];
 #pragma unroll
-            for (int mt = 0; mt < 4; ++mt) af[mt] = sw[(mt * 8 + g) * LDW + k0 + t];
-            const double *b = sB + (k0 + t) * ni;
+            for (int mt = 0; mt < MT; ++mt) af[mt] = sw[(mt * 8 + g) * LDW + k0 + t];
+            const double *b = sB + (k0 + t) * ldb;
 #pragma unroll
-            for (int nt = 0; nt < SYM_NTW; ++nt) bf[nt] = b[off1[nt]] * b[off2[nt]];
+            for (int nt = 0; nt < NTW; ++nt) bf[nt] = b[off1[nt]] * b[off2[nt]];
 #pragma unroll
-            for (int mt = 0; mt < 4; ++mt)
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int nt = 0; nt < SYM_NTW; ++nt) dmma_m8n8k4(acc[mt][nt], af[mt], bf[nt]);
+                for (int nt = 0; nt < NTW; ++nt) dmma_m8n8k4(acc[mt][nt], af[mt], bf[nt]);
         }
 
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt)
+        for (int mt = 0; mt < MT; ++mt)
         {
             const int rows = n_e - mt * 8 < 8 ? (n_e - mt * 8 > 0 ? n_e - mt * 8 : 0) : 8;   // valid elements of this row tile
-            double *img = (images & 1u) ? sStage1 : sStage0;
-            // the image buffer was last stored two images ago: all but the newest store have drained
-            if (tid == 0 && images >= 2) bulk_wait_read<1>();
+            double *img = reinterpret_cast<double *>(raw + L.stage_off + (images % C::IMAGES) * L.stage_bytes);
+            // the image buffer was last stored IMAGES images ago: all newer stores may still be draining
+            if (tid == 0 && images >= C::IMAGES) bulk_wait_read<C::IMAGES - 1>();
             __syncthreads();
             double *row = img + g * nc;
 #pragma unroll
-            for (int nt = 0; nt < SYM_NTW; ++nt)
+            for (int nt = 0; nt < NTW; ++nt)
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
                 {
-                    if (pos_d[nt][h] >= 0) row[pos_d[nt][h]] = acc[mt][nt][h];
-                    if (pos_m[nt][h] >= 0) row[pos_m[nt][h]] = acc[mt][nt][h];
+                    const int p = pos_d[nt][h];
+                    if (p >= 0)
+                    {
+                        const int i = p / ni, j = p - i * ni;
+                        row[p] = acc[mt][nt][h];
+                        row[j * ni + i] = acc[mt][nt][h];    // the mirror (the same slot on the diagonal)
+                    }
                 }
             fence_proxy_async();
             __syncthreads();
             double *dst = a.M + (e0 + mt * 8) * nc;
-            const bool whole = bulk_out && rows == 8 && ((8 * nc) % 2 == 0);
-            if (whole)
+            if (bulk_out && rows == 8)
             {
                 if (tid == 0)
                 {
@@ -370,7 +382,7 @@ rank1_gemm_sym_kernel(const Rank1Args a)
             }
             else
             {
-                for (int i = tid; i < rows * nc; i += SYM_THREADS) __stcs(dst + i, img[i]);
+                for (int i = tid; i < rows * nc; i += THREADS) __stcs(dst + i, img[i]);
                 if (tid == 0) bulk_commit();   // an empty group keeps the image/store numbering in step
             }
             ++images;
@@ -380,6 +392,9 @@ rank1_gemm_sym_kernel(const Rank1Args a)
     if (tid == 0) bulk_wait_all<0>();   // shared memory must outlive the stores that read it
 }
 
+typedef SymCfg<16, 3, 4, 2, 1> SymSmall;    // 512 threads, 32-element tiles, two images, one CTA per SM
+
+}
 
 extern "C" {
 
@@ -412,15 +427,17 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
 
     const size_t smem = sizeof(Smem);
     const int64_t n_tiles = (elements + ET - 1) / ET;
-    const bool symmetric = (B1 == B2 && ni == nj && op == ACRO_B200_OP_ASSIGN && ni * (ni + 1) / 2 <= SYM_MAX_COLS);
+    const bool symmetric = (B1 == B2 && ni == nj && op == ACRO_B200_OP_ASSIGN && ni * (ni + 1) / 2 <= SymSmall::MAX_COLS);
     if (symmetric)
     {
-        const SymLayout L = sym_layout(ni);
-        cudaError_t st = cudaFuncSetAttribute(rank1_gemm_sym_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        const SymLayout L = sym_layout(ni, SymSmall::TILE_E, SymSmall::IMAGES);
+        auto sym_kernel = rank1_gemm_sym_kernel<SymSmall>;
+        cudaError_t st = cudaFuncSetAttribute(sym_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
         if (st != cudaSuccess) return fail_cuda(st, "acro_b200_rank1_gemm (shared memory opt-in)");
-        int64_t g1 = sms;
-        if (g1 > n_tiles) g1 = n_tiles;
-        rank1_gemm_sym_kernel<<<static_cast<int>(g1), SYM_THREADS, L.total, as_stream(stream)>>>(args);
+        const int64_t sym_tiles = (elements + SymSmall::TILE_E - 1) / SymSmall::TILE_E;
+        int64_t g1 = static_cast<int64_t>(sms) * SymSmall::CTAS;
+        if (g1 > sym_tiles) g1 = sym_tiles;
+        sym_kernel<<<static_cast<int>(g1), SymSmall::THREADS, L.total, as_stream(stream)>>>(args);
         return launch_status("acro_b200_rank1_gemm (symmetric)");
     }
     auto kernel = rank1_gemm_kernel<4>;

@@ -118,7 +118,7 @@ class Tensor:
         return np.frombuffer(buf, dtype=np.float64).reshape(self.shape)
 
     def Retarget(self, hdata, ddata=None):
-        self._keep += [hdata, ddata]
+        self._keep = [None, hdata, ddata]      # the previous buffers are no longer referenced by this tensor
         dptr = ddata.data_ptr() if hasattr(ddata, "data_ptr") else ddata
         check(lib().acro_tensor_retarget(self._h, hdata.ctypes.data, dptr))
 

@@ -188,12 +188,30 @@ def run_ours(args):
     workloads = selected(args.workload)
     sessions, outs_dev, batches = [], [], []
     h2d = d2h = 0
-    # The end-to-end leg keeps every rank's inputs and results in pinned host memory; all
-    # ranks of the node share that memory, so refuse to pin more than half of what is free.
-    need = sum(sum(int(np.prod(shape)) * 8 for name, shape in w.shapes(local_batch(w, args, rank, world)).items()
-                   if w.tensors[name][2] != "tmp") for w in workloads) * world
+    # The end-to-end leg needs every rank's inputs and results in pinned host memory, and all
+    # ranks of the node share that memory.  Mode "all": everything pinned at once (allows a
+    # result's download to overlap the next configuration's upload) when that takes less than
+    # half of the free host memory; mode "one": one configuration pinned at a time; else skipped.
+    def host_bytes(w):
+        return sum(int(np.prod(shape)) * 8 for name, shape in w.shapes(local_batch(w, args, rank, world)).items()
+                   if w.tensors[name][2] != "tmp")
+    need_all = sum(host_bytes(w) for w in workloads) * world
+    need_one = max(host_bytes(w) for w in workloads) * world
     avail = host_memory_available()
-    pin_host = avail is None or need < 0.5 * avail
+    e2e_mode = "all" if (avail is None or need_all < 0.5 * avail) else ("one" if need_one < 0.5 * avail else "skip")
+    if args.e2e_mode != "auto":
+        e2e_mode = args.e2e_mode
+
+    def pinned_buffers(w, dev_t):
+        """Pinned host arrays for the inputs and results of one workload; inputs filled from the device."""
+        bufs = {}
+        for name in w.names("in") + w.names("out"):
+            bufs[name] = torch.empty(dev_t[name].shape, dtype=torch.float64, pin_memory=True)
+            if name in w.names("in"):
+                bufs[name].copy_(dev_t[name])
+        torch.cuda.synchronize()
+        return bufs
+
     for w in workloads:
         b = local_batch(w, args, rank, world)
         batches.append(b)
@@ -201,23 +219,17 @@ def run_ours(args):
         host = {}
         for name, shape in w.shapes(b).items():
             if name in dev_t:
-                pinned = torch.empty(shape, dtype=torch.float64, pin_memory=pin_host)
-                if pin_host:
-                    pinned.copy_(dev_t[name])
-                h2d += pinned.numel() * 8
-            elif w.tensors[name][2] == "out":
-                pinned = torch.empty(shape, dtype=torch.float64, pin_memory=pin_host)
-                dev_t[name] = torch.zeros(shape, dtype=torch.float64, device=dev)
-                d2h += pinned.numel() * 8
+                h2d += int(np.prod(shape)) * 8
             else:
-                # chain intermediates: transient, elided by the fused plan; a one-entry
-                # placeholder would not bind, so they get real (never touched) storage
-                pinned = torch.empty(shape, dtype=torch.float64)
-                dev_t[name] = torch.empty(shape, dtype=torch.float64, device=dev)
-            host[name] = pinned.numpy()
-            dev_t[name + "/pinned"] = pinned
+                # results, and chain intermediates (transient, elided by the fused plan; they
+                # still need real storage to bind)
+                dev_t[name] = torch.zeros(shape, dtype=torch.float64, device=dev)
+                if w.tensors[name][2] == "out":
+                    d2h += int(np.prod(shape)) * 8
+            # untouched pageable placeholder; the end-to-end leg retargets tensors to pinned buffers
+            host[name] = torch.empty(shape, dtype=torch.float64).numpy()
         torch.cuda.synchronize()
-        sess = Session(w, host, device={n: t for n, t in dev_t.items() if "/" not in n}, transient=True)
+        sess = Session(w, host, device=dict(dev_t), transient=True)
         sess.keep = dev_t
         sessions.append(sess)
         outs_dev.append({n: dev_t[n] for n in w.names("out")})
@@ -280,12 +292,14 @@ def run_ours(args):
         copy_stream.wait_event(ready)                   # the kernels that produce the result
         sess.fetch()                                     # MoveFromGPU of the result (D2H), synchronous for this thread
 
-    # Largest result first, so that its download overlaps the largest remaining upload.
-    e2e_order = sorted(range(len(workloads)), key=lambda i: -sum(outs_dev[i][n].numel() for n in outs_dev[i]))
+    def retarget(i, bufs):
+        w, sess = workloads[i], sessions[i]
+        for name, buf in bufs.items():
+            sess.t[name].Retarget(buf.numpy(), sess.keep[name])
 
-    def e2e_step():
+    def e2e_step(order):
         pending = []
-        for i in e2e_order:
+        for i in order:
             w, sess = workloads[i], sessions[i]
             for name in w.names("in"):
                 sess.t[name].SwitchFromGPU()          # the host copy is the fresh one again
@@ -300,14 +314,33 @@ def run_ours(args):
         for f in pending:
             f.result()
 
-    if pin_host:
-        e2e_step()
+    def timed_e2e(order):
+        e2e_step(order)
         barrier()
         w0 = time.perf_counter()
         for _ in range(e2e_steps):
-            e2e_step()
+            e2e_step(order)
         barrier()
-        e2e_ms = (time.perf_counter() - w0) * 1e3 / e2e_steps
+        return (time.perf_counter() - w0) * 1e3 / e2e_steps
+
+    if e2e_mode == "all":
+        keep_pinned = [pinned_buffers(w, sess.keep) for w, sess in zip(workloads, sessions)]
+        for i, bufs in enumerate(keep_pinned):
+            retarget(i, bufs)
+        # largest result first, so that its download overlaps the largest remaining upload
+        order = sorted(range(len(workloads)), key=lambda i: -sum(outs_dev[i][n].numel() for n in outs_dev[i]))
+        e2e_ms = timed_e2e(order)
+    elif e2e_mode == "one":
+        e2e_ms = 0.0
+        for i in range(len(workloads)):
+            bufs = pinned_buffers(workloads[i], sessions[i].keep)
+            retarget(i, bufs)
+            e2e_ms += timed_e2e([i])
+            # back to the pageable placeholders, so that the pinned buffers can be released
+            retarget(i, {n: torch.from_numpy(sessions[i].host[n]) for n in bufs})
+            for n in workloads[i].names("in"):
+                sessions[i].t[n].SwitchToGPU()
+            del bufs
     else:
         e2e_ms = float("nan")
 
@@ -363,10 +396,12 @@ def run_ours(args):
             "per_config": per_config,
             "roofline": roof,
             "e2e": ({"value": round(total_bytes / e2e_ms * 1e-6, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                     "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 2), "steps": e2e_steps} if pin_host else
+                     "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 2), "steps": e2e_steps,
+                     "pinned": "all configurations at once, download overlapped with the next upload" if e2e_mode == "all"
+                     else "one configuration at a time (host memory), upload and download serial"} if e2e_mode != "skip" else
                     {"value": None, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                     "skipped": "host memory: %.0f GB of pinned buffers needed on this node, %.0f GB available"
-                                % (need * 1e-9, (avail or 0) * 1e-9)}),
+                     "skipped": "host memory: %.0f GB of pinned buffers needed on this node for one configuration, %.0f GB available"
+                                % (need_one * 1e-9, (avail or 0) * 1e-9)}),
             "host_memory_available_gb": None if avail is None else round(avail * 1e-9, 1),
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
@@ -550,6 +585,8 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="multiplies every batch size (debugging; 1.0 = benchmark sizes)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-mode", default="auto", choices=["auto", "all", "one", "skip"],
+                    help="pinned host buffers for the end-to-end leg: all configurations at once, one at a time, or none")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

@@ -91,6 +91,10 @@ typedef struct acro_b200_generic_desc
 
 int acro_b200_generic_launch(const acro_b200_generic_desc *desc, double *out,
                              const double *const *inputs, void *stream);
+/* 1 when the launch would use the CTA-per-entry variant: at most 2048 output entries with at
+ * least 16384 terms each are summed by a whole CTA per entry in a fixed tree order (equal to
+ * the reference up to rounding, reproducible), because one thread per entry would idle the GPU. */
+int acro_b200_generic_uses_wide_kernel(const acro_b200_generic_desc *desc);
 
 /*
  * reduce_batch:  out[f] (op)= sum_{n<rows} A[n*F + f] * (w ? w[n] : 1),  f < F.

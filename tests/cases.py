@@ -42,6 +42,9 @@ REFERENCE_TEST_CASES = [
     ("accumulate", [("A_m_n+=B_m_j C_n_j", "A", ["B", "C"])], {"A": (3, 4), "B": (3, 5), "C": (4, 5)}, False),
     ("pointwise_2x2", [("D_p_m_n = S_p X_p_m_l Y_p_n_l", "D", ["S", "X", "Y"])],
      {"D": (37, 2, 2), "S": (37,), "X": (37, 2, 2), "Y": (37, 2, 2)}, False),
+    ("three_contracted", [("A_i = B_i_j_k_l C_j D_k_l", "A", ["B", "C", "D"])],
+     {"A": (6,), "B": (6, 3, 4, 5), "C": (3,), "D": (4, 5)}, False),
+    ("long_dot_products", [("S_a = X_n_a Y_n_a", "S", ["X", "Y"])], {"S": (3,), "X": (40000, 3), "Y": (40000, 3)}, False),
     ("pointwise_noscalar", [("D_p_m_n = X_p_m_l X_p_n_l", "D", ["X", "X"])], {"D": (300, 3, 3), "X": (300, 3, 3)}, False),
 ]
 

@@ -25,7 +25,7 @@ def field(text, key):
 
 def test_every_declared_symbol_is_exported_and_bound():
     header = open(os.path.join(ROOT, "include", "acro_b200.h")).read()
-    declared = set(re.findall(r"\b(acro_(?:b200|tensor|engine)_[a-z0-9_]+)\s*\(", header))
+    declared = set(re.findall(r"\b(acro_(?:b200|tensor|engine|index_mapping)_[a-z0-9_]+)\s*\(", header))
     assert len(declared) > 40
     handle = ctypes.CDLL(ab.LIB_PATH)
     for name in declared:
@@ -101,6 +101,13 @@ def test_family_selection():
     # the reference tests' D-tensor layout (m,n before the point indices) is not the pointwise layout
     text = ab.describe_plan(["D_e_m_n_k = W_e_k J_e_k_m_j J_e_k_n_j"], [[(10, 2, 2, 4), (10, 4), (10, 4, 2, 2), (10, 4, 2, 2)]])
     assert "family=generic" in text
+
+
+def test_long_contractions_with_few_outputs_get_a_cta_per_entry():
+    text = ab.describe_plan(["S_a = X_n_a Y_n_a"], [[(3,), (40000, 3), (40000, 3)]])
+    assert "family=generic" in text and "CTA per output entry" in text
+    text = ab.describe_plan(["S_a = X_n_a Y_n_a"], [[(3,), (400, 3), (400, 3)]])
+    assert "thread per output entry" in text
 
 
 def test_algorithmic_bytes_match_the_benchmark_definition():

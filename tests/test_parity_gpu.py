@@ -31,7 +31,7 @@ def torch():
 @pytest.mark.parametrize("case", cases.all_cases(), ids=lambda c: c[0])
 def test_engine_matches_reference_outputs(case):
     got, plan = gu.run_case_on_gpu(case)
-    exact = set(gu.families(plan)) <= gu.BIT_EXACT_FAMILIES
+    exact = set(gu.families(plan)) <= gu.BIT_EXACT_FAMILIES and "CTA per output entry" not in plan
     mags = None
     for n in cases.written(case):
         ref = GOLDEN["%s/out/%s" % (case[0], n)]
