@@ -15,6 +15,7 @@ CSRC = os.path.join(HERE, "csrc")
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT = 0, -1, -2, -3, -4
 MAX_LOOPS, MAX_INPUTS, MAX_POINT_LOOPS, MAX_SCALARS = 24, 12, 6, 6
+MAX_PEERS, IPC_HANDLE_BYTES = 16, 64
 OP_ASSIGN, OP_ADD, OP_SUB = 0, 1, 2
 
 
@@ -67,6 +68,13 @@ SIGNATURES = {
     "acro_b200_reduce_batch_scratch_bytes": (_SZ, [_I]),
     "acro_b200_reduce_batch_supported": (_I, [_I64, _I]),
     "acro_b200_reduce_batch": (_I, [_P, _P, _P, _I64, _I, _I, _P, _SZ, _P]),
+    "acro_b200_peer_group_create": (_I, [_I, _I, ctypes.POINTER(_P), _P]),
+    "acro_b200_peer_group_connect": (_I, [_P, _P]),
+    "acro_b200_peer_group_destroy": (_I, [_P]),
+    "acro_b200_peer_group_world": (_I, [_P]),
+    "acro_b200_peer_group_is_connected": (_I, [_P]),
+    "acro_b200_reduce_batch_allreduce": (_I, [_P, _P, _P, _I64, _I, _I, _P, _SZ, _P, _P]),
+    "acro_engine_set_peer_group": (_I, [_P, _P]),
     "acro_b200_reduce_batch_noalloc_max_f": (_I, []),
     "acro_b200_reduce_batch_noalloc": (_I, [_P, _P, _P, _I64, _I, _I, _P]),
     "acro_b200_pointwise_sym_supported": (_I, [ctypes.POINTER(PointwiseDesc)]),

@@ -115,9 +115,19 @@ void B200Executor::Run(std::vector<Tensor *> &outputs, std::vector<std::vector<T
             case plan::Family::ReduceBatch:
             {
                 const double *w = ins.size() > 1 ? ins[1]->GetDeviceData() : nullptr;
-                check_abi(acro_b200_reduce_batch(ins[0]->GetDeviceData(), w, out->GetDeviceData(), s.rows, s.sizes[0], s.op,
-                                                 Scratch, ScratchBytes, stream),
-                          "reduce_batch");
+                if (ThePeerGroup != nullptr)
+                {
+                    // the batch index is sharded over the ranks of the group: fused all-reduce
+                    check_abi(acro_b200_reduce_batch_allreduce(ins[0]->GetDeviceData(), w, out->GetDeviceData(), s.rows, s.sizes[0], s.op,
+                                                               Scratch, ScratchBytes, static_cast<acro_b200_peer_group *>(ThePeerGroup), stream),
+                              "reduce_batch_allreduce");
+                }
+                else
+                {
+                    check_abi(acro_b200_reduce_batch(ins[0]->GetDeviceData(), w, out->GetDeviceData(), s.rows, s.sizes[0], s.op,
+                                                     Scratch, ScratchBytes, stream),
+                              "reduce_batch");
+                }
                 break;
             }
             case plan::Family::PointwiseSym:

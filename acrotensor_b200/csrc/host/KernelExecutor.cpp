@@ -6,7 +6,7 @@ namespace acro
 {
 
 KernelExecutor::KernelExecutor(DimensionedMultiKernel *multi_kernel)
-    : OwnedMultiKernel(multi_kernel), MultiKernel(multi_kernel), FirstKernel(nullptr), TheCudaStream(nullptr)
+    : OwnedMultiKernel(multi_kernel), MultiKernel(multi_kernel), FirstKernel(nullptr), TheCudaStream(nullptr), ThePeerGroup(nullptr)
 {
     ACROBATIC_ASSERT(multi_kernel != nullptr, "An executor needs a kernel group.");
     if (MultiKernel->GetNumKernels() > 0) FirstKernel = MultiKernel->Kernels[0];
@@ -55,6 +55,7 @@ void KernelExecutor::ExecuteMulti(std::vector<Tensor *> &output, std::vector<std
     for (int ki = 0; ki < n; ++ki)
     {
         SubExecutors[ki]->SetCudaStream(TheCudaStream);
+        SubExecutors[ki]->SetPeerGroup(ThePeerGroup);
         SubExecutors[ki]->ExecuteSingle(output[ki], inputs[ki]);
     }
 }

@@ -5,17 +5,17 @@
 namespace acro
 {
 
-TensorEngine::TensorEngine() : IsMultiKernelLaunch(false), TheCudaStream(nullptr)
+TensorEngine::TensorEngine() : IsMultiKernelLaunch(false), TheCudaStream(nullptr), ThePeerGroup(nullptr)
 {
     SetExecutorType("Cuda");
 }
 
-TensorEngine::TensorEngine(const char *bare_exec_type) : IsMultiKernelLaunch(false), TheCudaStream(nullptr)
+TensorEngine::TensorEngine(const char *bare_exec_type) : IsMultiKernelLaunch(false), TheCudaStream(nullptr), ThePeerGroup(nullptr)
 {
     SetExecutorType(bare_exec_type);
 }
 
-TensorEngine::TensorEngine(std::string &exec_type) : IsMultiKernelLaunch(false), TheCudaStream(nullptr)
+TensorEngine::TensorEngine(std::string &exec_type) : IsMultiKernelLaunch(false), TheCudaStream(nullptr), ThePeerGroup(nullptr)
 {
     SetExecutorType(exec_type);
 }
@@ -78,6 +78,7 @@ void TensorEngine::operator()(std::string &kernel_str, Tensor *output, std::vect
     {
         KernelExecutor *executor = GetAddKernelExecutor();
         executor->SetCudaStream(TheCudaStream);
+        executor->SetPeerGroup(ThePeerGroup);
         executor->ExecuteSingle(output, inputs);
     }
 }
@@ -111,6 +112,7 @@ void TensorEngine::EndMultiKernelLaunch()
     if (MKLKernels.empty()) return;
     KernelExecutor *executor = GetAddKernelExecutor();
     executor->SetCudaStream(TheCudaStream);
+    executor->SetPeerGroup(ThePeerGroup);
     executor->ExecuteMulti(MKLOutputT, MKLInputT);
 }
 

@@ -262,6 +262,14 @@ int acro_engine_clear(acro_engine *e)
     });
 }
 
+int acro_engine_set_peer_group(acro_engine *e, acro_b200_peer_group *group)
+{
+    return guarded([&] {
+        if (e == nullptr) acro::throw_error("null engine handle");
+        e->te.SetPeerGroup(group);
+    });
+}
+
 int acro_engine_set_stream(acro_engine *e, void *stream)
 {
     return guarded([&] {

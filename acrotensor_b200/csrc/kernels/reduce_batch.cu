@@ -9,6 +9,7 @@
 //
 // Algorithmic HBM traffic: 8*F bytes of A and 8 bytes of w per row.
 #include "common.cuh"
+#include "peer.cuh"
 
 #include <mutex>
 
@@ -41,11 +42,53 @@ struct ReduceArgs
     int op;
     unsigned int *counter;
     double *partials;   // [gridDim.x][F]
+    int *wait_flag;     // raised when the bounded wait on the peers gives up
 };
 
-template <bool WEIGHTED, bool VECTOR>
+// Sum of this rank's total with the totals of all peer ranks, exchanged through the mailboxes
+// (see peer.cuh).  Called by the threads of the last CTA; `mine` is column t's total on this
+// rank (t < F).  Every rank adds the world totals in rank order, so all ranks obtain the same
+// bits.  The wait on the peers is bounded; when it runs out a flag is raised for the host and
+// the (then meaningless) result is still written, so nothing hangs.
+__device__ __forceinline__ double exchange_with_peers(const PeerView &pv, int t, int F, double mine, int *wait_flag)
+{
+    const int par = static_cast<int>(pv.seq & 1ull);
+    const size_t slot = (static_cast<size_t>(par) * pv.world + pv.rank) * kPeerMaxF;
+    if (t < F)
+    {
+        for (int p = 0; p < pv.world; ++p) pv.data[p][slot + t] = mine;   // remote stores over the peer mapping
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (t < pv.world)
+    {
+        // publish: this rank's data for call `seq` is complete in rank t's mailbox
+        volatile unsigned long long *remote = pv.flag[t] + static_cast<size_t>(par) * pv.world + pv.rank;
+        *remote = pv.seq;
+        // and wait until rank t's data has arrived in this rank's own mailbox
+        volatile unsigned long long *own = pv.flag[pv.rank] + static_cast<size_t>(par) * pv.world + t;
+        bool arrived = false;
+        for (unsigned int tries = 0; tries < (1u << 22); ++tries)
+        {
+            if (*own >= pv.seq) { arrived = true; break; }
+            __nanosleep(64);
+        }
+        if (!arrived) atomicExch(wait_flag, 1);
+        __threadfence_system();
+    }
+    __syncthreads();
+    double total = 0.0;
+    if (t < F)
+    {
+        const volatile double *box = pv.data[pv.rank] + static_cast<size_t>(par) * pv.world * kPeerMaxF;
+        for (int r = 0; r < pv.world; ++r) total += box[static_cast<size_t>(r) * kPeerMaxF + t];
+    }
+    return total;
+}
+
+template <bool WEIGHTED, bool VECTOR, bool PEERS>
 __global__ void __launch_bounds__(kMaxThreads)
-reduce_batch_kernel(const ReduceArgs a)
+reduce_batch_kernel(const ReduceArgs a, const PeerView pv)
 {
     extern __shared__ double lanes[];   // 2*T per-lane sums, reused by the final combine
     __shared__ bool is_last;
@@ -151,10 +194,14 @@ reduce_batch_kernel(const ReduceArgs a)
     for (int g = j; g < static_cast<int>(gridDim.x); g += J) s += __ldcg(a.partials + static_cast<int64_t>(g) * F + c);
     lanes[j * F + c] = s;
     __syncthreads();
+    double total = 0.0;
     if (t < F)
     {
-        double total = 0.0;
         for (int jj = 0; jj < J; ++jj) total += lanes[jj * F + t];
+    }
+    if (PEERS) total = exchange_with_peers(pv, t, F, total, a.wait_flag);
+    if (t < F)
+    {
         if (a.op == ACRO_B200_OP_ASSIGN) a.out[t] = total;
         else if (a.op == ACRO_B200_OP_ADD) a.out[t] += total;
         else a.out[t] -= total;
@@ -177,8 +224,8 @@ int acro_b200_reduce_batch_supported(int64_t rows, int F)
     return (F >= 1 && F <= kMaxThreads / 2 && rows >= 256) ? 1 : 0;
 }
 
-int acro_b200_reduce_batch(const double *A, const double *w, double *out, int64_t rows, int F, int op,
-                           double *scratch, size_t scratch_bytes, void *stream)
+static int launch_reduce(const double *A, const double *w, double *out, int64_t rows, int F, int op, double *scratch,
+                         size_t scratch_bytes, acro_b200_peer_group *group, void *stream)
 {
     if (A == nullptr || out == nullptr || scratch == nullptr) return fail_invalid("acro_b200_reduce_batch: null argument");
     if (rows < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_reduce_batch: bad rows or operator");
@@ -205,6 +252,17 @@ int acro_b200_reduce_batch(const double *A, const double *w, double *out, int64_
     args.op = op;
     args.counter = reinterpret_cast<unsigned int *>(scratch);
     args.partials = reinterpret_cast<double *>(reinterpret_cast<char *>(scratch) + kCounterBytes);
+    args.wait_flag = nullptr;
+    PeerView pv;
+    pv.world = 0;
+    if (group != nullptr)
+    {
+        if (acro_b200_peer_group_is_connected(group) != 1) return fail_invalid("acro_b200_reduce_batch_allreduce: the peer group is not connected");
+        if (F > kPeerMaxF) return fail_unsupported("acro_b200_reduce_batch_allreduce: row length exceeds the mailbox slot");
+        args.wait_flag = wait_flag_device_ptr();
+        if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_reduce_batch_allreduce (status flag)");
+        pv = next_peer_view(group);
+    }
 
     cudaStream_t s = as_stream(stream);
     cudaError_t status = cudaMemsetAsync(args.counter, 0, kCounterBytes, s);
@@ -212,17 +270,51 @@ int acro_b200_reduce_batch(const double *A, const double *w, double *out, int64_
     const size_t smem = 2 * static_cast<size_t>(T) * sizeof(double);
     const bool vec = aligned16(A);
     const int g = static_cast<int>(grid);
+    if (group != nullptr)
+    {
+        if (w != nullptr)
+        {
+            if (vec) reduce_batch_kernel<true, true, true><<<g, T, smem, s>>>(args, pv);
+            else reduce_batch_kernel<true, false, true><<<g, T, smem, s>>>(args, pv);
+        }
+        else
+        {
+            if (vec) reduce_batch_kernel<false, true, true><<<g, T, smem, s>>>(args, pv);
+            else reduce_batch_kernel<false, false, true><<<g, T, smem, s>>>(args, pv);
+        }
+        return launch_status("acro_b200_reduce_batch_allreduce");
+    }
     if (w != nullptr)
     {
-        if (vec) reduce_batch_kernel<true, true><<<g, T, smem, s>>>(args);
-        else reduce_batch_kernel<true, false><<<g, T, smem, s>>>(args);
+        if (vec) reduce_batch_kernel<true, true, false><<<g, T, smem, s>>>(args, pv);
+        else reduce_batch_kernel<true, false, false><<<g, T, smem, s>>>(args, pv);
     }
     else
     {
-        if (vec) reduce_batch_kernel<false, true><<<g, T, smem, s>>>(args);
-        else reduce_batch_kernel<false, false><<<g, T, smem, s>>>(args);
+        if (vec) reduce_batch_kernel<false, true, false><<<g, T, smem, s>>>(args, pv);
+        else reduce_batch_kernel<false, false, false><<<g, T, smem, s>>>(args, pv);
     }
     return launch_status("acro_b200_reduce_batch");
+}
+
+int acro_b200_reduce_batch(const double *A, const double *w, double *out, int64_t rows, int F, int op,
+                           double *scratch, size_t scratch_bytes, void *stream)
+{
+    return launch_reduce(A, w, out, rows, F, op, scratch, scratch_bytes, nullptr, stream);
+}
+
+// The reduction fused with the all-reduce over the ranks of a peer group: every rank streams
+// its own slab of rows, and the last CTA of each rank exchanges the F column totals with the
+// other ranks through their mailboxes (remote stores over NVLink, one bounded wait on local
+// memory) before it writes the result.  One kernel, no separate collective launch; all ranks
+// obtain bit-identical results.  Every rank of the group must make the same sequence of
+// calls; a rank that never calls makes the others give up after about a second with
+// ACRO_B200_ETIMEOUT reported by acro_b200_device_status().
+int acro_b200_reduce_batch_allreduce(const double *A, const double *w, double *out, int64_t rows, int F, int op,
+                                     double *scratch, size_t scratch_bytes, acro_b200_peer_group *group, void *stream)
+{
+    if (group == nullptr) return fail_invalid("acro_b200_reduce_batch_allreduce: null peer group");
+    return launch_reduce(A, w, out, rows, F, op, scratch, scratch_bytes, group, stream);
 }
 
 int acro_b200_reduce_batch_noalloc_max_f(void) { return kNoAllocMaxF; }

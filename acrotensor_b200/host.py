@@ -210,6 +210,30 @@ class IndexMapping:
         return inv, off
 
 
+class PeerGroup:
+    """The ranks (one process per GPU of a node) that hold slabs of a contracted batch index.
+    ``exchange(handle_bytes) -> [handle_bytes of every rank in rank order]`` is supplied by the
+    caller (e.g. torch.distributed.all_gather_object); world size 1 needs none."""
+
+    def __init__(self, world, rank, exchange=None):
+        h = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(_lib.IPC_HANDLE_BYTES)
+        check(lib().acro_b200_peer_group_create(int(world), int(rank), ctypes.byref(h), handle))
+        self._h = h
+        self.world, self.rank = int(world), int(rank)
+        if world > 1:
+            if exchange is None:
+                raise ValueError("a peer group of more than one rank needs an exchange function")
+            everyone = exchange(handle.raw)
+            assert len(everyone) == world and all(len(b) == _lib.IPC_HANDLE_BYTES for b in everyone)
+            check(lib().acro_b200_peer_group_connect(self._h, b"".join(everyone)))
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h is not None and _lib._lib is not None:
+            _lib._lib.acro_b200_peer_group_destroy(h)
+
+
 class TensorEngine:
     """acro::TensorEngine.  ``TE("S_i_j = A_n_i_j B_n", S, A, B)`` runs one contraction;
     Begin/EndMultiKernelLaunch record several and run them as one unit."""
@@ -274,6 +298,12 @@ class TensorEngine:
 
     def IsGPUAvailable(self):
         return isCudaReady()
+
+    def SetPeerGroup(self, group):
+        """Attach a PeerGroup (None detaches): contractions over a sharded, contracted batch index
+        then return the sum over all ranks (reduction and all-reduce fused in one kernel)."""
+        self._peer_group = group
+        check(lib().acro_engine_set_peer_group(self._h, group._h if group is not None else None))
 
     def SetCudaStream(self, stream_ptr):
         check(lib().acro_engine_set_stream(self._h, ctypes.c_void_p(stream_ptr or 0)))

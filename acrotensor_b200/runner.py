@@ -69,6 +69,22 @@ class Session:
         return te.EndMultiKernelLaunchDescribe()
 
 
+def make_peer_group():
+    """PeerGroup of all ranks of the initialised torch.distributed job (one process per GPU of one
+    node); the CUDA IPC handles of the mailboxes are exchanged with all_gather_object."""
+    import torch.distributed as dist
+    from .host import PeerGroup
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return PeerGroup(1, 0)
+
+    def exchange(mine):
+        everyone = [None] * dist.get_world_size()
+        dist.all_gather_object(everyone, mine)
+        return everyone
+
+    return PeerGroup(dist.get_world_size(), dist.get_rank(), exchange)
+
+
 def allreduce_partial(device_tensor, group=None):
     """Sum the per-rank partial results of a contracted batch index in place
     (torch.distributed; NCCL on GPUs, gloo in the CPU tests)."""

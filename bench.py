@@ -162,7 +162,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     import acrotensor_b200 as ab
-    from acrotensor_b200.runner import Session, allreduce_partial
+    from acrotensor_b200.runner import Session, allreduce_partial, make_peer_group
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -186,6 +186,8 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     workloads = selected(args.workload)
+    peer_group = None
+    use_nccl = world > 1 and args.allreduce == "nccl"
     sessions, outs_dev, batches = [], [], []
     h2d = d2h = 0
     # The end-to-end leg needs every rank's inputs and results in pinned host memory, and all
@@ -230,6 +232,10 @@ def run_ours(args):
             host[name] = torch.empty(shape, dtype=torch.float64).numpy()
         torch.cuda.synchronize()
         sess = Session(w, host, device=dict(dev_t), transient=True)
+        if w.batch_contracted and world > 1 and args.allreduce == "fused":
+            if peer_group is None:
+                peer_group = make_peer_group()
+            sess.te.SetPeerGroup(peer_group)     # reduction and all-reduce in one kernel, over NVLink peer memory
         sess.keep = dev_t
         sessions.append(sess)
         outs_dev.append({n: dev_t[n] for n in w.names("out")})
@@ -246,7 +252,7 @@ def run_ours(args):
             if events is not None:
                 events[i][0].record()
             sess.run()
-            if w.batch_contracted and world > 1:
+            if w.batch_contracted and use_nccl:
                 allreduce_partial(outs_dev[i][w.names("out")[0]])
             if events is not None:
                 events[i][1].record()
@@ -306,7 +312,7 @@ def run_ours(args):
             for name in w.names("out") + w.names("tmp"):
                 sess.t[name].SwitchFromGPU()
             sess.run()                                  # implicit MoveToGPU of every input (H2D), then the kernels
-            if w.batch_contracted and world > 1:
+            if w.batch_contracted and use_nccl:
                 allreduce_partial(outs_dev[i][w.names("out")[0]])
             ready = torch.cuda.Event()
             ready.record()
@@ -391,7 +397,9 @@ def run_ours(args):
             "config": {"workload": args.workload + (": cfg0..cfg4 back to back" if args.workload == "suite" else ""),
                        "batches_per_gpu": {w.key: b for w, b in zip(workloads, batches)},
                        "l2": "inputs_exceed_l2 (every configuration streams >= 1.6 GB per GPU)" if args.scale >= 1 else "scaled-down run",
-                       "parallelism": "batch slabs x%d, all-reduce only for the contracted batch index" % world},
+                       "parallelism": "batch slabs x%d, all-reduce only for the contracted batch index (%s)"
+                                      % (world, "none needed" if world == 1 else
+                                         ("fused into the reduction kernel over NVLink peer memory" if args.allreduce == "fused" else "NCCL"))},
             "gflops": round(total_flops / ms_per_step * 1e-6, 1),
             "per_config": per_config,
             "roofline": roof,
@@ -411,6 +419,9 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_baseline(workloads, args)
         print(json.dumps(line))
     pool.shutdown()
+    status = ab.lib().acro_b200_device_status()
+    if status != 0:
+        raise SystemExit("device status %d after the run: %s" % (status, ab.lib().acro_b200_last_error().decode()))
     if world > 1:
         dist.destroy_process_group()
 
@@ -587,6 +598,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-mode", default="auto", choices=["auto", "all", "one", "skip"],
                     help="pinned host buffers for the end-to-end leg: all configurations at once, one at a time, or none")
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: how the contracted batch index of the README reduction is summed over ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

@@ -35,6 +35,8 @@ class KernelExecutor
 
     // cudaStream_t passed as void*; nullptr selects the library-wide stream (setCudaStream).
     void SetCudaStream(void *cuda_stream) { TheCudaStream = cuda_stream; }
+    // acro_b200_peer_group* passed as void*: ranks that share a contracted batch index (nullptr = none).
+    void SetPeerGroup(void *peer_group) { ThePeerGroup = peer_group; }
 
     protected:
     void MoveTensorsFromGPU(Tensor *output, std::vector<Tensor *> &inputs);
@@ -47,6 +49,7 @@ class KernelExecutor
     DimensionedKernel *FirstKernel;
     std::vector<std::unique_ptr<KernelExecutor>> SubExecutors;
     void *TheCudaStream;
+    void *ThePeerGroup;
 };
 
 }

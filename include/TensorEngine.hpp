@@ -94,6 +94,11 @@ class TensorEngine
     // cudaStream_t (as void*) used by this engine's launches; nullptr = library-wide stream.
     void SetCudaStream(void *cuda_stream) { TheCudaStream = cuda_stream; }
 
+    // Multi-GPU, one process per GPU: attach the acro_b200_peer_group (as void*) of the ranks that
+    // hold slabs of a contracted batch index.  A contraction such as "S_i_j = A_n_i_j B_n" then
+    // returns, on every rank, the sum over all ranks' slabs (reduction and all-reduce in one kernel).
+    void SetPeerGroup(void *peer_group) { ThePeerGroup = peer_group; }
+
     private:
     TensorKernel *GetAddTensorKernel(std::string &kernel_str);
     DimensionedKernel *GetAddDimensionedKernel(TensorKernel *kernel, Tensor *output, std::vector<Tensor *> &inputs);
@@ -112,6 +117,7 @@ class TensorEngine
     std::vector<Tensor *> MKLOutputT;
     std::vector<std::vector<Tensor *>> MKLInputT;
     void *TheCudaStream;
+    void *ThePeerGroup;
 };
 
 }

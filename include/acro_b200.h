@@ -39,6 +39,8 @@ extern "C" {
 #define ACRO_B200_ECUDA (-3)        /* CUDA runtime failure, or no device */
 #define ACRO_B200_ETIMEOUT (-4)     /* a bounded device-side wait gave up */
 
+#define ACRO_B200_MAX_PEERS 16
+#define ACRO_B200_IPC_HANDLE_BYTES 64
 #define ACRO_B200_MAX_LOOPS 24
 #define ACRO_B200_MAX_INPUTS 12
 
@@ -111,6 +113,30 @@ size_t acro_b200_reduce_batch_scratch_bytes(int F);
 int acro_b200_reduce_batch_supported(int64_t rows, int F);
 int acro_b200_reduce_batch(const double *A, const double *w, double *out, int64_t rows, int F,
                            int op, double *scratch, size_t scratch_bytes, void *stream);
+
+/*
+ * Peer groups: the ranks (one process per GPU of one node) that hold slabs of a contracted
+ * batch index.  No counterpart in the reference, which is single-GPU (it is hard-wired to
+ * device 0, exec/CudaExecutor.cpp:21, util/CudaUtil.hpp:105).
+ *   create   allocates this rank's mailbox on the current device and returns its CUDA IPC handle
+ *            (ACRO_B200_IPC_HANDLE_BYTES bytes) to be exchanged by the host program
+ *            (MPI, torch.distributed ...);
+ *   connect  takes the world * ACRO_B200_IPC_HANDLE_BYTES handle bytes of all ranks, in rank order,
+ *            and maps the peers' mailboxes (NVLink peer access); world = 1 needs no connect.
+ * acro_b200_reduce_batch_allreduce is reduce_batch over this rank's rows followed, in the same
+ * kernel, by the sum over all ranks: each rank stores its F totals into every rank's mailbox and
+ * waits (bounded, on its own memory) for the others; every rank gets bit-identical results.
+ * All ranks must issue the same sequence of calls.
+ */
+typedef struct acro_b200_peer_group acro_b200_peer_group;
+int acro_b200_peer_group_create(int world, int rank, acro_b200_peer_group **out, unsigned char *handle_out);
+int acro_b200_peer_group_connect(acro_b200_peer_group *group, const unsigned char *all_handles);
+int acro_b200_peer_group_destroy(acro_b200_peer_group *group);
+int acro_b200_peer_group_world(const acro_b200_peer_group *group);
+int acro_b200_peer_group_is_connected(const acro_b200_peer_group *group);
+int acro_b200_reduce_batch_allreduce(const double *A, const double *w, double *out, int64_t rows, int F, int op,
+                                     double *scratch, size_t scratch_bytes, acro_b200_peer_group *group,
+                                     void *stream);
 
 /*
  * reduce_batch without any allocation.  No counterpart in the reference.
@@ -260,6 +286,10 @@ int acro_engine_end_multi(acro_engine *e);
 /* Ends the recording and returns the description of the fused plan instead of running it. */
 int acro_engine_end_multi_describe(acro_engine *e, char *buf, size_t buf_len);
 int acro_engine_clear(acro_engine *e);
+/* Attach (or detach with NULL) a peer group: from then on a contraction whose contracted batch
+ * index is planned as reduce_batch returns the sum over all ranks' slabs (fused all-reduce).
+ * The engine does not own the group. */
+int acro_engine_set_peer_group(acro_engine *e, acro_b200_peer_group *group);
 /* cudaStream_t as void*; applies to later launches of this engine. */
 int acro_engine_set_stream(acro_engine *e, void *stream);
 /* IndexMapping(domain_size, range_size), tensor/IndexMapping.hpp:14-48.  acro_index_mapping_data
