@@ -68,7 +68,7 @@ __device__ __forceinline__ double exchange_with_peers(const PeerView &pv, int t,
         // and wait until rank t's data has arrived in this rank's own mailbox
         volatile unsigned long long *own = pv.flag[pv.rank] + static_cast<size_t>(par) * pv.world + t;
         bool arrived = false;
-        for (unsigned int tries = 0; tries < (1u << 22); ++tries)
+        for (unsigned int tries = 0; tries < (1u << 21); ++tries)   // about a second
         {
             if (*own >= pv.seq) { arrived = true; break; }
             __nanosleep(64);

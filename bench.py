@@ -258,6 +258,7 @@ def run_ours(args):
                 events[i][1].record()
 
     make_resident()
+    barrier()      # all ranks enter the first step together (the fused all-reduce waits at most about a second)
     plans = [sess.plan_text() for sess in sessions]
     launches_per_step = sum(p.count("\nstep ") for p in plans)
     for _ in range(args.warmup):

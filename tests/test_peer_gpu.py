@@ -96,3 +96,42 @@ def test_two_ranks_on_two_gpus(tmp_path):
     assert np.array_equal(r0[:-1], r1[:-1])                       # every rank holds the same bits
     for call in range(4):
         assert oracle.parity_error(r0[call], ref, mags) <= TOL
+
+
+def _rank_absent_peer(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+    from acrotensor_b200.runner import make_peer_group
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        group = make_peer_group()
+        outcome = []
+        if rank == 0:
+            # rank 1 never makes the matching call: the bounded wait must run out, report
+            # ETIMEOUT to the host and leave the context usable
+            a = torch.ones(4096, 9, dtype=torch.float64, device="cuda")
+            out = torch.zeros(9, dtype=torch.float64, device="cuda")
+            nbytes = lib().acro_b200_reduce_batch_scratch_bytes(9)
+            scratch = torch.empty(nbytes // 8 + 1, dtype=torch.float64, device="cuda")
+            p = lambda t: ctypes.c_void_p(t.data_ptr())
+            check(lib().acro_b200_reduce_batch_allreduce(p(a), None, p(out), 4096, 9, 0, p(scratch), nbytes, group._h, None))
+            outcome.append(lib().acro_b200_device_status())
+            outcome.append(lib().acro_b200_device_status())          # the flag is cleared by the first read
+            check(lib().acro_b200_reduce_batch(p(a), None, p(out), 4096, 9, 0, p(scratch), nbytes, None))
+            outcome.append(float(out[0].item()))
+            np.save(os.path.join(out_dir, "timeout.npy"), np.array(outcome, dtype=np.float64))
+        dist.barrier()       # rank 1 keeps its mailbox alive until rank 0 is done
+    finally:
+        dist.destroy_process_group()
+
+
+def test_absent_peer_times_out_instead_of_hanging(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mp.spawn(_rank_absent_peer, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    first, second, plain = np.load(os.path.join(str(tmp_path), "timeout.npy"))
+    assert int(first) == _lib.ETIMEOUT and int(second) == _lib.OK and plain == 4096.0
