@@ -201,8 +201,12 @@ rank1_gemm_kernel(const Rank1Args a)
 // Results are scattered, entry (i,j) and its mirror (j,i), into a shared-memory image of 8
 // full element matrices, which then leaves as ONE contiguous bulk store; IMAGES such images
 // alternate so the store of one row tile drains while the next is scattered.
-// Measured on B200 (E = 2^18, 27 x 27): 16 warps x 3 column tiles x 4 row tiles, 2 images,
-// one CTA per SM: 0.583 ms; 8 warps x 6 x 2, 1 image, two CTAs per SM: 0.652 ms.
+// Measured on B200 (E = 2^18, 27 x 27): 8 warps x 6 column tiles x 2 row tiles, 1 image, two
+// CTAs per SM (one CTA's scatter/store overlaps the other's tensor-core loop): 0.566 ms;
+// 16 warps x 3 x 4, 2 images, one CTA per SM: 0.579 ms; 8 warps x 6 x 4, 2 images, one CTA:
+// 0.601 ms.  Recomputing the mirror positions in the epilogue (integer divisions) instead of
+// keeping them in registers costs 0.08 ms.  Shared-memory wavefronts (fragment loads, scatter,
+// bulk store) are about as many as tensor-pipe cycles, which is what bounds all three.
 template <int WARPS_, int NTW_, int MT_, int IMAGES_, int CTAS_>
 struct SymCfg
 {
@@ -221,7 +225,7 @@ __host__ __device__ inline SymLayout sym_layout(int ni, int tile_e, int images)
 {
     SymLayout l;
     l.ldb = ni;
-    while (l.ldb % 8 != 4) ++l.ldb;                        // row stride = 4 mod 8 doubles: conflict-free fragment loads
+    while (l.ldb % 8 != 4) ++l.ldb;                        // row stride = 4 mod 8 doubles: fewer bank conflicts in fragment loads
     const int w_bytes = 2 * tile_e * LDW * 8;
     l.b_off = w_bytes;
     const int b_bytes = ((QN * l.ldb * 8 + 127) / 128) * 128;
@@ -267,7 +271,7 @@ rank1_gemm_sym_kernel(const Rank1Args a)
         j = row + (c - start);
     };
     int off1[NTW], off2[NTW];    // B-fragment column of this lane
-    int pos_d[NTW][2];           // where this lane's two C-fragment columns go (-1: padding)
+    int pos_d[NTW][2], pos_m[NTW][2];   // where this lane's two C-fragment columns and their mirrors go (-1: padding)
 #pragma unroll
     for (int nt = 0; nt < NTW; ++nt)
     {
@@ -279,12 +283,13 @@ rank1_gemm_sym_kernel(const Rank1Args a)
         for (int h = 0; h < 2; ++h)
         {
             const int cc = cbase + 2 * t + h;
-            pos_d[nt][h] = -1;
+            pos_d[nt][h] = pos_m[nt][h] = -1;
             if (cc < n_cols)
             {
                 int i, j;
                 unpack(cc, i, j);
                 pos_d[nt][h] = i * ni + j;
+                if (i != j) pos_m[nt][h] = j * ni + i;
             }
         }
     }
@@ -361,13 +366,8 @@ rank1_gemm_sym_kernel(const Rank1Args a)
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
                 {
-                    const int p = pos_d[nt][h];
-                    if (p >= 0)
-                    {
-                        const int i = p / ni, j = p - i * ni;
-                        row[p] = acc[mt][nt][h];
-                        row[j * ni + i] = acc[mt][nt][h];    // the mirror (the same slot on the diagonal)
-                    }
+                    if (pos_d[nt][h] >= 0) row[pos_d[nt][h]] = acc[mt][nt][h];
+                    if (pos_m[nt][h] >= 0) row[pos_m[nt][h]] = acc[mt][nt][h];
                 }
             fence_proxy_async();
             __syncthreads();
@@ -392,7 +392,7 @@ rank1_gemm_sym_kernel(const Rank1Args a)
     if (tid == 0) bulk_wait_all<0>();   // shared memory must outlive the stores that read it
 }
 
-typedef SymCfg<16, 3, 4, 2, 1> SymSmall;    // 512 threads, 32-element tiles, two images, one CTA per SM
+typedef SymCfg<8, 6, 2, 1, 2> SymSmall;    // 256 threads, 16-element tiles, one image, two CTAs per SM
 
 }
 
