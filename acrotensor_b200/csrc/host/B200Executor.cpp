@@ -109,7 +109,7 @@ void B200Executor::Run(std::vector<Tensor *> &outputs, std::vector<std::vector<T
                 if (s.zero_fill_first) check_abi(acro_b200_fill(out->GetDeviceData(), out->GetSize64(), 0.0, stream), "fill");
                 const double *ptrs[ACRO_B200_MAX_INPUTS];
                 for (std::size_t i = 0; i < ins.size(); ++i) ptrs[i] = ins[i]->GetDeviceData();
-                check_abi(acro_b200_generic_launch(&s.generic, out->GetDeviceData(), ptrs, stream), "generic_launch");
+                check_abi(acro_b200_generic_launch(&s.generic, out->GetDeviceData(), ptrs, Scratch, ScratchBytes, stream), "generic_launch");
                 break;
             }
             case plan::Family::ReduceBatch:

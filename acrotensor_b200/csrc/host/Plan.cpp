@@ -117,7 +117,7 @@ Step plan_generic(DimensionedKernel &k, int ki)
     s.bytes = io_bytes(k);
     s.flops = outer_points * terms * k.GetNumInputVars();   // (n_in - 1) multiplies + 1 add per term
     std::ostringstream note;
-    if (acro_b200_generic_uses_wide_kernel(&g)) note << "CTA per output entry (fixed-order tree sum): " << outer_points << " entries x " << terms << " terms";
+    if (acro_b200_generic_uses_wide_kernel(&g)) note << "CTA per range of terms (fixed-order tree sum): " << outer_points << " entries x " << terms << " terms";
     else note << "thread per output entry: " << outer_points << " entries x " << terms << " terms";
     s.note = note.str();
     return s;
@@ -486,6 +486,10 @@ Program BuildProgram(DimensionedMultiKernel &mk, bool allow_elision)
         if (s.family == Family::ReduceBatch)
         {
             p.scratch_bytes = std::max(p.scratch_bytes, acro_b200_reduce_batch_scratch_bytes(s.sizes[0]));
+        }
+        if (s.family == Family::Generic)
+        {
+            p.scratch_bytes = std::max(p.scratch_bytes, acro_b200_generic_scratch_bytes(&s.generic));
         }
     }
     return p;

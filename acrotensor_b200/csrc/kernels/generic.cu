@@ -158,65 +158,131 @@ generic_contract_kernel(const __grid_constant__ acro_b200_generic_desc d, double
     }
 }
 
-// Few output entries but a long contraction (for example "S_a = X_n_a Y_n_a"): one CTA per
-// output entry, the terms split over its threads and combined in a fixed order.  The sum
-// order differs from the reference's sequential one (results agree to rounding, and are
-// reproducible run to run); the one-thread-per-entry kernel above would leave the GPU idle.
+// Few output entries but a long contraction (for example "S_a = X_n_a Y_n_a"): the terms of
+// every output entry are cut into `chunks` contiguous ranges, one CTA per (entry, range); the
+// threads of a CTA take interleaved terms (coalesced for a unit-stride innermost index) and
+// combine in a fixed tree order; the CTA that finishes last for an entry (ticket counter in
+// scratch) adds the range sums in ascending order.  The sum order differs from the
+// reference's sequential one (results agree to rounding and are reproducible run to run);
+// the one-thread-per-entry kernel above would leave the GPU idle on such shapes.
 constexpr int kWideThreads = 256;
+constexpr int kWideMaxChunks = 256;
+constexpr int kWideMaxOuter = 2048;
+
+struct WideScratch
+{
+    unsigned int *counters;   // [outer_points]
+    double *partials;         // [outer_points][chunks]
+    int chunks;
+    int64_t chunk_terms;
+};
+
+__device__ __forceinline__ double block_tree_sum(double v, double *partial)
+{
+    partial[threadIdx.x] = v;
+    __syncthreads();
+    for (int width = kWideThreads / 2; width > 0; width >>= 1)
+    {
+        if (threadIdx.x < width) partial[threadIdx.x] = __dadd_rn(partial[threadIdx.x], partial[threadIdx.x + width]);
+        __syncthreads();
+    }
+    const double total = partial[0];
+    __syncthreads();
+    return total;
+}
 
 template <int N_IN>
 __global__ void __launch_bounds__(kWideThreads)
 generic_wide_kernel(const __grid_constant__ acro_b200_generic_desc d, double *__restrict__ out,
-                    const __grid_constant__ InputPointers ins, int64_t outer_points, int64_t terms)
+                    const __grid_constant__ InputPointers ins, int64_t terms, const WideScratch ws)
 {
     __shared__ double partial[kWideThreads];
+    __shared__ bool is_last;
     const int n_in = N_IN > 0 ? N_IN : d.n_inputs;
     const int n_outer = d.n_outer, n_loops = d.n_loops;
-    for (int64_t point = blockIdx.x; point < outer_points; point += gridDim.x)
+    const int64_t point = blockIdx.x / ws.chunks;
+    const int chunk = blockIdx.x % ws.chunks;
+
+    int64_t out_off = 0;
+    int64_t base[ACRO_B200_MAX_INPUTS];
+#pragma unroll
+    for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v) base[v] = 0;
+    int64_t rest = point;
+    for (int l = n_outer - 1; l >= 0; --l)
     {
-        int64_t out_off = 0;
-        int64_t base[ACRO_B200_MAX_INPUTS];
-#pragma unroll
-        for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v) base[v] = 0;
-        int64_t rest = point;
-        for (int l = n_outer - 1; l >= 0; --l)
-        {
-            const int64_t idx = rest % d.extent[l];
-            rest /= d.extent[l];
-            out_off += idx * d.out_step[l];
-            advance<N_IN>(base, d, l, idx, n_in);
-        }
-        double acc = 0.0;
-        for (int64_t term = threadIdx.x; term < terms; term += kWideThreads)
-        {
-            int64_t off[ACRO_B200_MAX_INPUTS];
-#pragma unroll
-            for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v) off[v] = base[v];
-            int64_t r = term;
-            for (int l = n_loops - 1; l >= n_outer; --l)
-            {
-                const int64_t idx = r % d.extent[l];
-                r /= d.extent[l];
-                advance<N_IN>(off, d, l, idx, n_in);
-            }
-            acc = __dadd_rn(acc, product_at<N_IN>(ins, off, n_in));
-        }
-        partial[threadIdx.x] = acc;
-        __syncthreads();
-        for (int width = kWideThreads / 2; width > 0; width >>= 1)
-        {
-            if (threadIdx.x < width) partial[threadIdx.x] = __dadd_rn(partial[threadIdx.x], partial[threadIdx.x + width]);
-            __syncthreads();
-        }
-        if (threadIdx.x == 0)
-        {
-            const double total = partial[0];
-            if (d.op == ACRO_B200_OP_ASSIGN) out[out_off] = total;
-            else if (d.op == ACRO_B200_OP_ADD) out[out_off] = __dadd_rn(out[out_off], total);
-            else out[out_off] = __dsub_rn(out[out_off], total);
-        }
-        __syncthreads();
+        const int64_t idx = rest % d.extent[l];
+        rest /= d.extent[l];
+        out_off += idx * d.out_step[l];
+        advance<N_IN>(base, d, l, idx, n_in);
     }
+
+    const int64_t t_begin = chunk * ws.chunk_terms;
+    const int64_t t_end = t_begin + ws.chunk_terms < terms ? t_begin + ws.chunk_terms : terms;
+    double acc = 0.0;
+    for (int64_t term = t_begin + threadIdx.x; term < t_end; term += kWideThreads)
+    {
+        int64_t off[ACRO_B200_MAX_INPUTS];
+#pragma unroll
+        for (int v = 0; v < ACRO_B200_MAX_INPUTS; ++v) off[v] = base[v];
+        uint32_t r = static_cast<uint32_t>(term);            // the launcher guarantees terms < 2^31
+        for (int l = n_loops - 1; l > n_outer; --l)
+        {
+            const uint32_t ext = static_cast<uint32_t>(d.extent[l]);
+            const uint32_t q = r / ext;
+            advance<N_IN>(off, d, l, static_cast<int64_t>(r - q * ext), n_in);
+            r = q;
+        }
+        advance<N_IN>(off, d, n_outer, static_cast<int64_t>(r), n_in);   // outermost contracted loop: no division
+        acc = __dadd_rn(acc, product_at<N_IN>(ins, off, n_in));
+    }
+    const double chunk_sum = block_tree_sum(acc, partial);
+
+    if (threadIdx.x == 0)
+    {
+        ws.partials[point * ws.chunks + chunk] = chunk_sum;
+        __threadfence();
+        is_last = (atomicAdd(ws.counters + point, 1u) == static_cast<unsigned int>(ws.chunks - 1));
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // chunks <= kWideThreads: thread c fetches range sum c; ascending-index tree
+    const double mine = threadIdx.x < ws.chunks ? __ldcg(ws.partials + point * ws.chunks + threadIdx.x) : 0.0;
+    const double total = block_tree_sum(mine, partial);
+    if (threadIdx.x == 0)
+    {
+        if (d.op == ACRO_B200_OP_ASSIGN) out[out_off] = total;
+        else if (d.op == ACRO_B200_OP_ADD) out[out_off] = __dadd_rn(out[out_off], total);
+        else out[out_off] = __dsub_rn(out[out_off], total);
+        ws.counters[point] = 0u;
+    }
+}
+
+// How the wide kernel cuts the work: 0 chunks = use the thread-per-entry kernel.
+struct WidePlan
+{
+    int chunks = 0;
+    int64_t chunk_terms = 0;
+    int64_t outer_points = 1, terms = 1;
+    size_t counter_bytes = 0, total_bytes = 0;
+};
+
+WidePlan wide_plan(const acro_b200_generic_desc &d)
+{
+    WidePlan p;
+    for (int l = 0; l < d.n_loops && l < ACRO_B200_MAX_LOOPS; ++l) (l < d.n_outer ? p.outer_points : p.terms) *= d.extent[l];
+    if (d.n_loops <= d.n_outer || p.outer_points > kWideMaxOuter || p.terms < 16384 || p.terms >= 0x7fffffffLL) return p;
+    // enough CTAs to fill the machine, at least 4096 terms each
+    int64_t want = (4 * 148 + p.outer_points - 1) / p.outer_points;
+    const int64_t by_size = p.terms / 4096;
+    if (want > by_size) want = by_size;
+    if (want > kWideMaxChunks) want = kWideMaxChunks;
+    if (want < 1) want = 1;
+    p.chunk_terms = (p.terms + want - 1) / want;
+    p.chunks = static_cast<int>((p.terms + p.chunk_terms - 1) / p.chunk_terms);
+    p.counter_bytes = ((static_cast<size_t>(p.outer_points) * sizeof(unsigned int) + 255) / 256) * 256;
+    p.total_bytes = p.counter_bytes + static_cast<size_t>(p.outer_points) * p.chunks * sizeof(double);
+    return p;
 }
 
 template <int N_IN>
@@ -235,16 +301,19 @@ void launch_thread_per_entry(const acro_b200_generic_desc &d, double *out, const
 
 }
 
-// 1 when the launch would use the CTA-per-entry kernel: few output entries, long contraction.
+// 1 when the launch would use the CTA-per-range kernel: few output entries, long contraction.
 extern "C" int acro_b200_generic_uses_wide_kernel(const acro_b200_generic_desc *desc)
 {
-    if (desc == nullptr) return 0;
-    int64_t outer_points = 1, terms = 1;
-    for (int l = 0; l < desc->n_loops && l < ACRO_B200_MAX_LOOPS; ++l) (l < desc->n_outer ? outer_points : terms) *= desc->extent[l];
-    return (outer_points <= 2048 && terms >= 16384) ? 1 : 0;
+    return (desc != nullptr && wide_plan(*desc).chunks > 0) ? 1 : 0;
 }
 
-extern "C" int acro_b200_generic_launch(const acro_b200_generic_desc *desc, double *out, const double *const *inputs, void *stream)
+extern "C" size_t acro_b200_generic_scratch_bytes(const acro_b200_generic_desc *desc)
+{
+    return desc != nullptr ? wide_plan(*desc).total_bytes : 0;
+}
+
+extern "C" int acro_b200_generic_launch(const acro_b200_generic_desc *desc, double *out, const double *const *inputs,
+                                        double *scratch, size_t scratch_bytes, void *stream)
 {
     if (desc == nullptr || out == nullptr || inputs == nullptr) return fail_invalid("acro_b200_generic_launch: null argument");
     if (desc->n_loops < 1 || desc->n_loops > ACRO_B200_MAX_LOOPS || desc->n_outer < 0 || desc->n_outer > desc->n_loops ||
@@ -267,16 +336,25 @@ extern "C" int acro_b200_generic_launch(const acro_b200_generic_desc *desc, doub
     if (sm_count() <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_generic_launch");
 
     cudaStream_t s = as_stream(stream);
-    if (acro_b200_generic_uses_wide_kernel(desc))
+    const WidePlan wp = wide_plan(*desc);
+    if (wp.chunks > 0)
     {
-        const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
-        const int grid = static_cast<int>(outer_points < cap ? outer_points : cap);
+        if (scratch == nullptr || scratch_bytes < wp.total_bytes) return fail_invalid("acro_b200_generic_launch: scratch buffer missing or too small (see acro_b200_generic_scratch_bytes)");
+        if ((reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) return fail_invalid("acro_b200_generic_launch: scratch must be 256-byte aligned");
+        WideScratch ws;
+        ws.counters = reinterpret_cast<unsigned int *>(scratch);
+        ws.partials = reinterpret_cast<double *>(reinterpret_cast<char *>(scratch) + wp.counter_bytes);
+        ws.chunks = wp.chunks;
+        ws.chunk_terms = wp.chunk_terms;
+        cudaError_t status = cudaMemsetAsync(ws.counters, 0, wp.counter_bytes, s);
+        if (status != cudaSuccess) return fail_cuda(status, "acro_b200_generic_launch (counter reset)");
+        const int grid = static_cast<int>(outer_points * wp.chunks);
         switch (desc->n_inputs)
         {
-            case 1: generic_wide_kernel<1><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, outer_points, terms); break;
-            case 2: generic_wide_kernel<2><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, outer_points, terms); break;
-            case 3: generic_wide_kernel<3><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, outer_points, terms); break;
-            default: generic_wide_kernel<0><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, outer_points, terms); break;
+            case 1: generic_wide_kernel<1><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, terms, ws); break;
+            case 2: generic_wide_kernel<2><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, terms, ws); break;
+            case 3: generic_wide_kernel<3><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, terms, ws); break;
+            default: generic_wide_kernel<0><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, terms, ws); break;
         }
         return launch_status("acro_b200_generic_launch (wide)");
     }

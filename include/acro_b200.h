@@ -92,11 +92,17 @@ typedef struct acro_b200_generic_desc
 } acro_b200_generic_desc;
 
 int acro_b200_generic_launch(const acro_b200_generic_desc *desc, double *out,
-                             const double *const *inputs, void *stream);
-/* 1 when the launch would use the CTA-per-entry variant: at most 2048 output entries with at
- * least 16384 terms each are summed by a whole CTA per entry in a fixed tree order (equal to
- * the reference up to rounding, reproducible), because one thread per entry would idle the GPU. */
+                             const double *const *inputs, double *scratch, size_t scratch_bytes,
+                             void *stream);
+/* Shapes with at most 2048 output entries and at least 16384 terms each (for example
+ * "S_a = X_n_a Y_n_a") use a second variant, because one thread per entry would idle the GPU:
+ * the terms of an entry are cut into ranges, one CTA per range, combined in a fixed order
+ * (equal to the reference up to rounding, reproducible run to run).  It needs
+ * acro_b200_generic_scratch_bytes(desc) bytes of 256-byte aligned device scratch (0 for the
+ * one-thread-per-entry variant, which accepts scratch = NULL); calls sharing one scratch
+ * buffer must not overlap on the device. */
 int acro_b200_generic_uses_wide_kernel(const acro_b200_generic_desc *desc);
+size_t acro_b200_generic_scratch_bytes(const acro_b200_generic_desc *desc);
 
 /*
  * reduce_batch:  out[f] (op)= sum_{n<rows} A[n*F + f] * (w ? w[n] : 1),  f < F.

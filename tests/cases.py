@@ -45,6 +45,8 @@ REFERENCE_TEST_CASES = [
     ("three_contracted", [("A_i = B_i_j_k_l C_j D_k_l", "A", ["B", "C", "D"])],
      {"A": (6,), "B": (6, 3, 4, 5), "C": (3,), "D": (4, 5)}, False),
     ("long_dot_products", [("S_a = X_n_a Y_n_a", "S", ["X", "Y"])], {"S": (3,), "X": (40000, 3), "Y": (40000, 3)}, False),
+    ("long_two_loop_sums", [("S_a_b += X_n_m_a Y_m_n_b W_m", "S", ["X", "Y", "W"])],
+     {"S": (2, 3), "X": (300, 70, 2), "Y": (70, 300, 3), "W": (70,)}, False),
     ("pointwise_noscalar", [("D_p_m_n = X_p_m_l X_p_n_l", "D", ["X", "X"])], {"D": (300, 3, 3), "X": (300, 3, 3)}, False),
 ]
 

@@ -105,7 +105,7 @@ def test_family_selection():
 
 def test_long_contractions_with_few_outputs_get_a_cta_per_entry():
     text = ab.describe_plan(["S_a = X_n_a Y_n_a"], [[(3,), (40000, 3), (40000, 3)]])
-    assert "family=generic" in text and "CTA per output entry" in text
+    assert "family=generic" in text and "CTA per range of terms" in text
     text = ab.describe_plan(["S_a = X_n_a Y_n_a"], [[(3,), (400, 3), (400, 3)]])
     assert "thread per output entry" in text
 

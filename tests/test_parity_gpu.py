@@ -31,7 +31,7 @@ def torch():
 @pytest.mark.parametrize("case", cases.all_cases(), ids=lambda c: c[0])
 def test_engine_matches_reference_outputs(case):
     got, plan = gu.run_case_on_gpu(case)
-    exact = set(gu.families(plan)) <= gu.BIT_EXACT_FAMILIES and "CTA per output entry" not in plan
+    exact = set(gu.families(plan)) <= gu.BIT_EXACT_FAMILIES and "CTA per range of terms" not in plan
     mags = None
     for n in cases.written(case):
         ref = GOLDEN["%s/out/%s" % (case[0], n)]
@@ -279,15 +279,15 @@ def test_generic_kernel_descriptor_checks(torch):
     x = torch.zeros(8, dtype=torch.float64, device="cuda")
     ptrs = (ctypes.c_void_p * 1)(x.data_ptr())
     d.n_loops, d.n_outer, d.n_inputs, d.op = 0, 0, 1, 0
-    assert lib().acro_b200_generic_launch(ctypes.byref(d), gu.dev_ptr(x), ptrs, None) == _lib.EINVAL
+    assert lib().acro_b200_generic_launch(ctypes.byref(d), gu.dev_ptr(x), ptrs, None, 0, None) == _lib.EINVAL
     d.n_loops, d.n_outer = 1, 1
     d.extent[0] = 0
-    assert lib().acro_b200_generic_launch(ctypes.byref(d), gu.dev_ptr(x), ptrs, None) == _lib.EINVAL
+    assert lib().acro_b200_generic_launch(ctypes.byref(d), gu.dev_ptr(x), ptrs, None, 0, None) == _lib.EINVAL
     d.extent[0], d.out_step[0] = 8, 1
     d.in_step[0][0] = 1
     x2 = torch.arange(8, dtype=torch.float64, device="cuda")
     ptrs = (ctypes.c_void_p * 1)(x2.data_ptr())
-    check(lib().acro_b200_generic_launch(ctypes.byref(d), gu.dev_ptr(x), ptrs, None))
+    check(lib().acro_b200_generic_launch(ctypes.byref(d), gu.dev_ptr(x), ptrs, None, 0, None))
     assert bool((x == x2).all())
 
 
