@@ -1,4 +1,5 @@
-// batched_gemm: C_e = A_e * B_e for a batch of small dense fp64 matrices (64 x 64 x 64).
+// batched_gemm: C_e = A_e * B_e for a batch of small dense fp64 matrices (N x N x N, N = 64 or 32).
+// The description below gives the N = 64 figures.
 //
 // Persistent CTAs (one per SM, 8 warps) walk over the batch.  A_e and B_e (32 KB each,
 // contiguous) are copied asynchronously (16-byte cp.async, one 512-byte matrix row per warp
@@ -26,14 +27,14 @@ using namespace acro_b200_detail;
 namespace
 {
 
-constexpr int N = 64;                 // matrix extent
-constexpr int LD = N + 4;             // padded row: 68 doubles (544 bytes, a 16-byte multiple)
 constexpr int STAGES = 3;
 constexpr int NT = 256;               // 8 warps
-constexpr int MAT = N * LD;           // doubles per padded matrix
 
+template <int N>
 struct Smem
 {
+    static constexpr int LD = N + 4;      // padded row (N = 64: 68 doubles = 544 bytes, a 16-byte multiple)
+    static constexpr int MAT = N * LD;    // doubles per padded matrix
     double A[STAGES][MAT];
     double B[STAGES][MAT];
     uint64_t full[STAGES];
@@ -58,30 +59,36 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
 
 // Every thread copies its 16 chunks of element e into slot `stage` and attaches an arrival
 // on the slot's "full" barrier to the completion of those copies.
-__device__ __forceinline__ void issue_element_load(Smem &s, const GemmArgs &a, int64_t e, int stage)
+template <int N>
+__device__ __forceinline__ void issue_element_load(Smem<N> &s, const GemmArgs &a, int64_t e, int stage)
 {
+    constexpr int LD = Smem<N>::LD;
+    constexpr int ROW_CHUNKS = N / 2;          // 16-byte chunks per matrix row
     const int tid = threadIdx.x;
     const double *ga = a.A + e * N * N, *gb = a.B + e * N * N;
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < N * ROW_CHUNKS / NT; ++i)
     {
         const int c = tid + i * NT;            // 16-byte chunk number inside A (and inside B)
-        const int row = c >> 5, col = (c & 31) * 2;
+        const int row = c / ROW_CHUNKS, col = (c % ROW_CHUNKS) * 2;
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&s.A[stage][row * LD + col])), "l"(ga + c * 2) : "memory");
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&s.B[stage][row * LD + col])), "l"(gb + c * 2) : "memory");
     }
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&s.full[stage])) : "memory");
 }
 
-__global__ void __launch_bounds__(NT, 1)
-batched_gemm64_kernel(const GemmArgs a)
+template <int N>
+__global__ void __launch_bounds__(NT, N == 64 ? 1 : 4)
+batched_gemm_kernel(const GemmArgs a)
 {
+    constexpr int LD = Smem<N>::LD;
+    constexpr int MT = N / 32, NTL = N / 16;      // 8-row / 8-column accumulator tiles per warp
     extern __shared__ __align__(128) unsigned char raw[];
-    Smem &s = *reinterpret_cast<Smem *>(raw);
+    Smem<N> &s = *reinterpret_cast<Smem<N> *>(raw);
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 32;
+    const int m0 = (warp >> 1) * (N / 4), n0 = (warp & 1) * (N / 2);
 
     if (tid == 0)
     {
@@ -129,33 +136,33 @@ batched_gemm64_kernel(const GemmArgs a)
 
         const double *sa = s.A[stage];
         const double *sb = s.B[stage];
-        double c[2][4][2];
+        double c[MT][NTL][2];
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) c[mt][nt][0] = c[mt][nt][1] = 0.0;
+            for (int nt = 0; nt < NTL; ++nt) c[mt][nt][0] = c[mt][nt][1] = 0.0;
 
 #pragma unroll 4
         for (int k0 = 0; k0 < N; k0 += 4)
         {
-            double af[2], bf[4];
+            double af[MT], bf[NTL];
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) af[mt] = sa[(m0 + mt * 8 + g) * LD + k0 + t];
+            for (int mt = 0; mt < MT; ++mt) af[mt] = sa[(m0 + mt * 8 + g) * LD + k0 + t];
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) bf[nt] = sb[(k0 + t) * LD + n0 + nt * 8 + g];
+            for (int nt = 0; nt < NTL; ++nt) bf[nt] = sb[(k0 + t) * LD + n0 + nt * 8 + g];
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) dmma_m8n8k4(c[mt][nt], af[mt], bf[nt]);
+                for (int nt = 0; nt < NTL; ++nt) dmma_m8n8k4(c[mt][nt], af[mt], bf[nt]);
         }
         if (a.async_copy) mbar_arrive(&s.empty[stage]);   // this thread no longer reads the slot
 
         // C rows leave as 64-byte segments per quad (two doubles per lane)
         double *gc = a.C + e * N * N;
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
+            for (int nt = 0; nt < NTL; ++nt)
             {
                 double *dst = gc + (m0 + mt * 8 + g) * N + n0 + nt * 8 + 2 * t;
                 double v0 = c[mt][nt][0], v1 = c[mt][nt][1];
@@ -171,13 +178,13 @@ batched_gemm64_kernel(const GemmArgs a)
 
 extern "C" {
 
-int acro_b200_batched_gemm_supported(int m, int n, int k) { return (m == N && n == N && k == N) ? 1 : 0; }
+int acro_b200_batched_gemm_supported(int m, int n, int k) { return (m == n && n == k && (m == 64 || m == 32)) ? 1 : 0; }
 
 int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int op, void *stream)
 {
     if (A == nullptr || B == nullptr || C == nullptr) return fail_invalid("acro_b200_batched_gemm: null argument");
     if (batch < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_batched_gemm: bad batch or operator");
-    if (!acro_b200_batched_gemm_supported(m, n, k)) return fail_unsupported("acro_b200_batched_gemm: only 64 x 64 x 64 is instantiated");
+    if (!acro_b200_batched_gemm_supported(m, n, k)) return fail_unsupported("acro_b200_batched_gemm: only 64^3 and 32^3 are instantiated");
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_batched_gemm");
 
@@ -191,12 +198,13 @@ int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t 
     if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_batched_gemm (status flag)");
     args.async_copy = (aligned16(A) && aligned16(B)) ? 1 : 0;
 
-    const size_t smem = sizeof(Smem);
-    cudaError_t status = cudaFuncSetAttribute(batched_gemm64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    auto kernel = m == 64 ? batched_gemm_kernel<64> : batched_gemm_kernel<32>;
+    const size_t smem = m == 64 ? sizeof(Smem<64>) : sizeof(Smem<32>);
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (status != cudaSuccess) return fail_cuda(status, "acro_b200_batched_gemm (shared memory opt-in)");
-    int64_t grid = sms;
+    int64_t grid = static_cast<int64_t>(sms) * (m == 64 ? 1 : 4);
     if (grid > batch) grid = batch;
-    batched_gemm64_kernel<<<static_cast<int>(grid), NT, smem, as_stream(stream)>>>(args);
+    kernel<<<static_cast<int>(grid), NT, smem, as_stream(stream)>>>(args);
     return launch_status("acro_b200_batched_gemm");
 }
 

@@ -29,7 +29,7 @@ using namespace acro_b200_detail;
 namespace
 {
 
-constexpr int QN = 64;                 // contracted extent
+constexpr int QN = 64;                 // largest contracted extent (any multiple of 4 up to this)
 constexpr int ET = 32;                 // elements per CTA tile (4 row tiles of 8)
 constexpr int LDW = QN + 4;            // padded W row
 constexpr int NTHREADS = 256;
@@ -53,6 +53,7 @@ struct Rank1Args
     const double *B2;
     double *M;
     int64_t elements;
+    int q;          // contracted extent, a multiple of 4, <= QN
     int ni, nj;
     int op;
     int *wait_flag;
@@ -67,10 +68,10 @@ __device__ __forceinline__ void issue_w_load(Smem &s, const Rank1Args &a, int64_
     {
         const int64_t left = a.elements - e0;
         const int n_e = left < ET ? static_cast<int>(left) : ET;
-        if (threadIdx.x == 0) mbar_arrive_expect_tx(&s.full[buf], n_e * QN * 8);
+        if (threadIdx.x == 0) mbar_arrive_expect_tx(&s.full[buf], n_e * a.q * 8);
         __syncwarp();
         if (static_cast<int>(threadIdx.x) < n_e)
-            bulk_load(&s.W[buf][threadIdx.x * LDW], a.W + (e0 + threadIdx.x) * QN, QN * 8, &s.full[buf]);
+            bulk_load(&s.W[buf][threadIdx.x * LDW], a.W + (e0 + threadIdx.x) * a.q, a.q * 8, &s.full[buf]);
     }
 }
 
@@ -96,8 +97,8 @@ rank1_gemm_kernel(const Rank1Args a)
         mbar_init(&s.full[1], 1);
         fence_mbar_init();
     }
-    for (int i = tid; i < QN * ni; i += NTHREADS) s.B1[i] = a.B1[i];
-    for (int i = tid; i < QN * nj; i += NTHREADS) s.B2[i] = a.B2[i];
+    for (int i = tid; i < a.q * ni; i += NTHREADS) s.B1[i] = a.B1[i];
+    for (int i = tid; i < a.q * nj; i += NTHREADS) s.B2[i] = a.B2[i];
     __syncthreads();
 
     int64_t tile = blockIdx.x;
@@ -119,7 +120,7 @@ rank1_gemm_kernel(const Rank1Args a)
         }
         else
         {
-            for (int i = tid; i < n_e * QN; i += NTHREADS) s.W[buf][(i / QN) * LDW + (i % QN)] = __ldcs(a.W + e0 * QN + i);
+            for (int i = tid; i < n_e * a.q; i += NTHREADS) s.W[buf][(i / a.q) * LDW + (i % a.q)] = __ldcs(a.W + e0 * a.q + i);
             __syncthreads();
         }
         const double *sw = s.W[buf];
@@ -144,7 +145,7 @@ rank1_gemm_kernel(const Rank1Args a)
                 for (int nt = 0; nt < NTG; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
 
 #pragma unroll 2
-            for (int k0 = 0; k0 < QN; k0 += 4)
+            for (int k0 = 0; k0 < a.q; k0 += 4)
             {
                 double af[4], bf[NTG];
 #pragma unroll
@@ -260,7 +261,7 @@ rank1_gemm_sym_kernel(const Rank1Args a)
         mbar_init(&full[1], 1);
         fence_mbar_init();
     }
-    for (int i = tid; i < QN * ni; i += THREADS) sB[(i / ni) * ldb + (i % ni)] = a.B1[i];
+    for (int i = tid; i < a.q * ni; i += THREADS) sB[(i / ni) * ldb + (i % ni)] = a.B1[i];
     __syncthreads();
 
     // packed column c -> (i, j), row-major upper triangle; fixed per thread for the whole kernel
@@ -301,9 +302,9 @@ rank1_gemm_sym_kernel(const Rank1Args a)
         {
             const int64_t left = a.elements - e0;
             const int n_e = left < TE ? static_cast<int>(left) : TE;
-            if (tid == 0) mbar_arrive_expect_tx(&full[buf], n_e * QN * 8);
+            if (tid == 0) mbar_arrive_expect_tx(&full[buf], n_e * a.q * 8);
             __syncwarp();
-            if (tid < n_e) bulk_load(sW + buf * TE * LDW + tid * LDW, a.W + (e0 + tid) * QN, QN * 8, &full[buf]);
+            if (tid < n_e) bulk_load(sW + buf * TE * LDW + tid * LDW, a.W + (e0 + tid) * a.q, a.q * 8, &full[buf]);
         }
     };
 
@@ -327,7 +328,7 @@ rank1_gemm_sym_kernel(const Rank1Args a)
         }
         else
         {
-            for (int i = tid; i < n_e * QN; i += THREADS) sW[buf * TE * LDW + (i / QN) * LDW + (i % QN)] = __ldcs(a.W + e0 * QN + i);
+            for (int i = tid; i < n_e * a.q; i += THREADS) sW[buf * TE * LDW + (i / a.q) * LDW + (i % a.q)] = __ldcs(a.W + e0 * a.q + i);
             __syncthreads();
         }
         const double *sw = sW + buf * TE * LDW;
@@ -338,7 +339,7 @@ rank1_gemm_sym_kernel(const Rank1Args a)
 #pragma unroll
             for (int nt = 0; nt < NTW; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
 #pragma unroll 2
-        for (int k0 = 0; k0 < QN; k0 += 4)
+        for (int k0 = 0; k0 < a.q; k0 += 4)
         {
             double af[MT], bf[NTW];
 #pragma unroll
@@ -400,7 +401,7 @@ extern "C" {
 
 int acro_b200_rank1_gemm_supported(int q, int ni, int nj)
 {
-    return (q == QN && ni >= 1 && ni <= MAXN && nj >= 1 && nj <= MAXN) ? 1 : 0;
+    return (q >= 4 && q <= QN && q % 4 == 0 && ni >= 1 && ni <= MAXN && nj >= 1 && nj <= MAXN) ? 1 : 0;
 }
 
 int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, double *M, int64_t elements, int q, int ni, int nj,
@@ -408,7 +409,7 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
 {
     if (W == nullptr || B1 == nullptr || B2 == nullptr || M == nullptr) return fail_invalid("acro_b200_rank1_gemm: null argument");
     if (elements < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_rank1_gemm: bad element count or operator");
-    if (!acro_b200_rank1_gemm_supported(q, ni, nj)) return fail_unsupported("acro_b200_rank1_gemm: needs q = 64 and 1 <= ni, nj <= 32");
+    if (!acro_b200_rank1_gemm_supported(q, ni, nj)) return fail_unsupported("acro_b200_rank1_gemm: needs q a multiple of 4 up to 64 and 1 <= ni, nj <= 32");
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_rank1_gemm");
 
@@ -418,6 +419,7 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
     args.B2 = B2;
     args.M = M;
     args.elements = elements;
+    args.q = q;
     args.ni = ni;
     args.nj = nj;
     args.op = op;

@@ -25,22 +25,29 @@ using namespace acro_b200_detail;
 namespace
 {
 
-constexpr int P = 4;
-constexpr int Q = 5;
-constexpr int ET = 32;                    // elements per tile
-constexpr int NT = ET * Q;                // threads per CTA
-constexpr int U_ELEM = P * P * P;         // 64
-constexpr int W_ELEM = Q * Q * Q;         // 125
-constexpr int U_STRIDE = U_ELEM + 2;      // padded slot, 16-byte multiple
-constexpr int Y_STRIDE = P * P * Q + 5;   // 85: conflict-free for both access patterns
-constexpr int Y_ROW = P * Q;              // 20 doubles per (element, i1) row of Y2; V reuses the first 16
+constexpr int ET = 32;   // elements per tile
 
+// Compile-time geometry for P dofs and Q quadrature points per direction.
+template <int P_, int Q_, int CTAS_>
+struct Geo
+{
+    static constexpr int P = P_, Q = Q_, CTAS = CTAS_;
+    static constexpr int NT = ET * Q;                                 // threads per CTA
+    static constexpr int U_ELEM = P * P * P, W_ELEM = Q * Q * Q;
+    static constexpr int U_STRIDE = U_ELEM + 2 - (U_ELEM % 2);        // padded, even (16-byte multiple)
+    static constexpr bool U_BULK = (U_ELEM % 2 == 0);                 // an element of U is a 16-byte multiple
+    static constexpr int Y_ROW = P * Q;                               // Y2 row of one (element, i1); V reuses the first P*P
+    static constexpr int Y_MIN = P * P * Q;
+    static constexpr int Y_STRIDE = Y_MIN + ((Q - Y_MIN % 16) % 16 + 16) % 16;   // = Q mod 16: plane owners of a half warp hit distinct banks
+};
+
+template <class G>
 struct Smem
 {
-    double U[ET * U_STRIDE];
-    double W[ET * W_ELEM];
-    double Y[ET * Y_STRIDE];
-    double B[Q * P];
+    double U[ET * G::U_STRIDE];
+    double W[ET * G::W_ELEM];
+    double Y[ET * G::Y_STRIDE];
+    double B[G::Q * G::P];
     uint64_t bar;
 };
 
@@ -55,25 +62,29 @@ struct MassArgs
     int use_bulk;   // operands are 16-byte aligned: bulk copies allowed
 };
 
-__device__ __forceinline__ void issue_tile_load(Smem &s, const MassArgs &a, int64_t tile, int64_t n_tiles_full)
+template <class G>
+__device__ __forceinline__ void issue_tile_load(Smem<G> &s, const MassArgs &a, int64_t tile, int64_t n_tiles_full)
 {
     // Only whole tiles travel by bulk copy (sizes and addresses stay 16-byte multiples).
     if (!a.use_bulk || tile >= n_tiles_full) return;
     if (threadIdx.x < 32)
     {
         const int64_t e0 = tile * ET;
-        if (threadIdx.x == 0) mbar_arrive_expect_tx(&s.bar, ET * (U_ELEM + W_ELEM) * 8);
+        if (threadIdx.x == 0) mbar_arrive_expect_tx(&s.bar, ET * ((G::U_BULK ? G::U_ELEM : 0) + G::W_ELEM) * 8);
         __syncwarp();
-        bulk_load(s.U + threadIdx.x * U_STRIDE, a.U + (e0 + threadIdx.x) * U_ELEM, U_ELEM * 8, &s.bar);
-        if (threadIdx.x == 0) bulk_load(s.W, a.W + e0 * W_ELEM, ET * W_ELEM * 8, &s.bar);
+        if (G::U_BULK) bulk_load(s.U + threadIdx.x * G::U_STRIDE, a.U + (e0 + threadIdx.x) * G::U_ELEM, G::U_ELEM * 8, &s.bar);
+        if (threadIdx.x == 0) bulk_load(s.W, a.W + e0 * G::W_ELEM, ET * G::W_ELEM * 8, &s.bar);
     }
 }
 
-__global__ void __launch_bounds__(NT, 3)
+template <class G>
+__global__ void __launch_bounds__(G::NT, G::CTAS)
 sumfact_mass_kernel(const MassArgs a)
 {
+    constexpr int P = G::P, Q = G::Q, NT = G::NT;
+    constexpr int U_ELEM = G::U_ELEM, W_ELEM = G::W_ELEM, U_STRIDE = G::U_STRIDE, Y_STRIDE = G::Y_STRIDE, Y_ROW = G::Y_ROW;
     extern __shared__ __align__(128) unsigned char raw[];
-    Smem &s = *reinterpret_cast<Smem *>(raw);
+    Smem<G> &s = *reinterpret_cast<Smem<G> *>(raw);
     const int tid = threadIdx.x;
     const int64_t n_tiles = (a.elements + ET - 1) / ET;
     const int64_t n_tiles_full = a.elements / ET;
@@ -108,18 +119,22 @@ sumfact_mass_kernel(const MassArgs a)
         const int64_t e0 = tile * ET;
         const int64_t left = a.elements - e0;
         const int n_e = left < ET ? static_cast<int>(left) : ET;
+        const bool by_bulk = a.use_bulk && tile < n_tiles_full;
 
-        if (a.use_bulk && tile < n_tiles_full)
+        if (!by_bulk || !G::U_BULK)
+        {
+            // U by plain coalesced loads into the padded slots (ragged / unaligned tile, or odd element size)
+            for (int i = tid; i < n_e * U_ELEM; i += NT) s.U[(i / U_ELEM) * U_STRIDE + (i % U_ELEM)] = __ldcs(a.U + e0 * U_ELEM + i);
+        }
+        if (!by_bulk)
+        {
+            for (int i = tid; i < n_e * W_ELEM; i += NT) s.W[i] = __ldcs(a.W + e0 * W_ELEM + i);
+        }
+        if (!by_bulk || !G::U_BULK) __syncthreads();
+        if (by_bulk)
         {
             if (!mbar_wait(&s.bar, parity)) atomicExch(a.wait_flag, 1);
             parity ^= 1u;
-        }
-        else
-        {
-            // ragged or unaligned tile: plain coalesced loads into the same layout
-            for (int i = tid; i < n_e * U_ELEM; i += NT) s.U[(i / U_ELEM) * U_STRIDE + (i % U_ELEM)] = __ldcs(a.U + e0 * U_ELEM + i);
-            for (int i = tid; i < n_e * W_ELEM; i += NT) s.W[i] = __ldcs(a.W + e0 * W_ELEM + i);
-            __syncthreads();
         }
 
         if (eb < n_e)
@@ -132,12 +147,27 @@ sumfact_mass_kernel(const MassArgs a)
 #pragma unroll
                 for (int i2 = 0; i2 < P; ++i2)
                 {
-                    const double2 lo = *reinterpret_cast<const double2 *>(u + (i1 * P + i2) * P);
-                    const double2 hi = *reinterpret_cast<const double2 *>(u + (i1 * P + i2) * P + 2);
-                    double acc = brow[0] * lo.x;
-                    acc = fma(brow[1], lo.y, acc);
-                    acc = fma(brow[2], hi.x, acc);
-                    acc = fma(brow[3], hi.y, acc);
+                    const double *ur = u + (i1 * P + i2) * P;
+                    double uv[P];
+                    if (P % 2 == 0)
+                    {
+                        // even P: rows of U start on 16-byte boundaries in the padded slot
+#pragma unroll
+                        for (int i3 = 0; i3 < P; i3 += 2)
+                        {
+                            const double2 pair = *reinterpret_cast<const double2 *>(ur + i3);
+                            uv[i3] = pair.x;
+                            uv[i3 + 1 < P ? i3 + 1 : i3] = pair.y;
+                        }
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int i3 = 0; i3 < P; ++i3) uv[i3] = ur[i3];
+                    }
+                    double acc = brow[0] * uv[0];
+#pragma unroll
+                    for (int i3 = 1; i3 < P; ++i3) acc = fma(brow[i3], uv[i3], acc);
                     t1[i1][i2] = acc;
                 }
             // stage 2: T2_i1_k2 = sum_i2 B_k2_i2 T1_i1_i2
@@ -215,7 +245,7 @@ sumfact_mass_kernel(const MassArgs a)
         }
         __syncthreads();   // V tile complete (inside the Y buffer)
 
-        // contiguous coalesced store of the V tile: entry i of element e sits at e*85 + (i/16)*20 + i%16
+        // contiguous coalesced store of the V tile: entry r of element e sits at e*Y_STRIDE + (r/P^2)*Y_ROW + r%P^2
         double *dst = a.V + e0 * U_ELEM;
         for (int i = tid; i < n_e * U_ELEM; i += NT)
         {
@@ -226,17 +256,35 @@ sumfact_mass_kernel(const MassArgs a)
     }
 }
 
+typedef Geo<4, 5, 3> Geo45;   // p = 3 hexahedra: 4 dofs, 5 quadrature points per direction
+typedef Geo<3, 4, 4> Geo34;   // p = 2
+typedef Geo<2, 3, 6> Geo23;   // p = 1
+
+template <class G>
+int launch_mass(const MassArgs &args, int sms, cudaStream_t stream)
+{
+    const size_t smem = sizeof(Smem<G>);
+    // The opt-in is a per-device function attribute; setting it again is a cheap host call.
+    cudaError_t status = cudaFuncSetAttribute(sumfact_mass_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_sumfact_mass (shared memory opt-in)");
+    const int64_t n_tiles = (args.elements + ET - 1) / ET;
+    int64_t grid = static_cast<int64_t>(sms) * G::CTAS;
+    if (grid > n_tiles) grid = n_tiles;
+    sumfact_mass_kernel<G><<<static_cast<int>(grid), G::NT, smem, stream>>>(args);
+    return launch_status("acro_b200_sumfact_mass");
+}
+
 }
 
 extern "C" {
 
-int acro_b200_sumfact_mass_supported(int p, int q) { return (p == P && q == Q) ? 1 : 0; }
+int acro_b200_sumfact_mass_supported(int p, int q) { return ((p == 4 && q == 5) || (p == 3 && q == 4) || (p == 2 && q == 3)) ? 1 : 0; }
 
 int acro_b200_sumfact_mass(const double *B, const double *U, const double *W, double *V, int64_t elements, int p, int q, void *stream)
 {
     if (B == nullptr || U == nullptr || W == nullptr || V == nullptr) return fail_invalid("acro_b200_sumfact_mass: null argument");
     if (elements < 1) return fail_invalid("acro_b200_sumfact_mass: element count must be positive");
-    if (!acro_b200_sumfact_mass_supported(p, q)) return fail_unsupported("acro_b200_sumfact_mass: only P=4, Q=5 is instantiated");
+    if (!acro_b200_sumfact_mass_supported(p, q)) return fail_unsupported("acro_b200_sumfact_mass: instantiated for (p, q) = (2, 3), (3, 4), (4, 5)");
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_sumfact_mass");
 
@@ -249,16 +297,10 @@ int acro_b200_sumfact_mass(const double *B, const double *U, const double *W, do
     args.wait_flag = wait_flag_device_ptr();
     if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_sumfact_mass (status flag)");
     args.use_bulk = (aligned16(U) && aligned16(W)) ? 1 : 0;
-
-    const size_t smem = sizeof(Smem);
-    // The opt-in is a per-device function attribute; setting it again is a cheap host call.
-    cudaError_t status = cudaFuncSetAttribute(sumfact_mass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_sumfact_mass (shared memory opt-in)");
-    const int64_t n_tiles = (elements + ET - 1) / ET;
-    int64_t grid = static_cast<int64_t>(sms) * 3;
-    if (grid > n_tiles) grid = n_tiles;
-    sumfact_mass_kernel<<<static_cast<int>(grid), NT, smem, as_stream(stream)>>>(args);
-    return launch_status("acro_b200_sumfact_mass");
+    cudaStream_t s = as_stream(stream);
+    if (p == 4) return launch_mass<Geo45>(args, sms, s);
+    if (p == 3) return launch_mass<Geo34>(args, sms, s);
+    return launch_mass<Geo23>(args, sms, s);
 }
 
 }

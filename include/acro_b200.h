@@ -195,7 +195,7 @@ int acro_b200_pointwise_sym(const acro_b200_pointwise_desc *desc, const double *
  * rank1_gemm:  M[e,i,j] (op)= sum_{q<Q} W[e,q] * B1[q,i] * B2[q,j]   (batched element mass matrices,
  * "M_e_i_j = W_e_q B_q_i B_q_j").  One GEMM  [elements x Q] * [Q x ni*nj]  whose right operand
  * B1[q,i]*B2[q,j] is formed on the fly; fp64 tensor cores (mma.sync m8n8k4).  Instantiated
- * for Q = 64 and ni, nj <= 32.  HBM traffic 8*(Q + ni*nj) bytes per element, 2*Q*ni*nj flops.
+ * for Q a multiple of 4 up to 64 and ni, nj <= 32.  HBM traffic 8*(Q + ni*nj) bytes per element, 2*Q*ni*nj flops.
  * Replaces the generated kernel (one block per element, serial 64-term sums per thread,
  * exec/CudaExecutor.cpp:193-204,520-523).
  */
@@ -205,7 +205,7 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
 
 /*
  * batched_gemm:  C[e,i,j] (op)= sum_{k} A[e,i,k] * B[e,k,j]  for a batch of dense row-major
- * matrices ("C_e_i_j = A_e_i_k B_e_k_j").  Instantiated for m = n = k = 64: persistent CTAs,
+ * matrices ("C_e_i_j = A_e_i_k B_e_k_j").  Instantiated for m = n = k = 64 and 32: persistent CTAs,
  * three-stage asynchronous bulk-copy ring for A_e and B_e, fp64 tensor cores.  HBM traffic
  * 8*(mk + kn + mn) bytes and 2mnk flops per element.  Replaces the generated kernel (scalar
  * DFMA from global memory, no tiling, exec/CudaExecutor.cpp:520-604).
@@ -219,7 +219,8 @@ int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t 
  *   V_e_i1_i2_i3 = sum B_k3_i3 B_k2_i2 B_k1_i1 W_e_k1_k2_k3 (sum B_k1_j1 B_k2_j2 B_k3_j3 U_e_j1_j2_j3),
  * evaluated stage by stage (contract i3, i2, i1, scale by W, contract k1, k2, k3) with every
  * intermediate kept in registers / shared memory.  B is [q][p], U and V are [elements][p][p][p],
- * W is [elements][q][q][q].  HBM traffic: 8*(2p^3 + q^3) bytes per element.  Replaces the
+ * W is [elements][q][q][q]; instantiated for (p, q) = (2,3), (3,4), (4,5).  HBM traffic:
+ * 8*(2p^3 + q^3) bytes per element.  Replaces the
  * reference's fused multi-kernel launch (exec/CudaExecutor.cpp:69-102,286-323), which still
  * writes every intermediate tensor to global memory (:536).
  */

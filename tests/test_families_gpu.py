@@ -37,17 +37,17 @@ def status_ok():
     assert lib().acro_b200_device_status() == _lib.OK
 
 
-@pytest.mark.parametrize("elements,ni,nj,op,offset", [
-    (32, 27, 27, 0, 0), (33, 27, 27, 0, 0), (1, 27, 27, 0, 0), (100, 27, 27, 1, 0), (257, 27, 27, 2, 0),
-    (64, 5, 7, 0, 0), (95, 32, 32, 0, 0), (70, 27, 27, 0, 1), (10000, 27, 27, 0, 0), (40, 27, 27, 0, 2), (75, 1, 1, 0, 0),
-    (50, 2, 2, 1, 0),
+@pytest.mark.parametrize("elements,ni,nj,op,offset,q", [
+    (32, 27, 27, 0, 0, 64), (33, 27, 27, 0, 0, 64), (1, 27, 27, 0, 0, 64), (100, 27, 27, 1, 0, 64), (257, 27, 27, 2, 0, 64),
+    (64, 5, 7, 0, 0, 64), (95, 32, 32, 0, 0, 64), (70, 27, 27, 0, 1, 64), (10000, 27, 27, 0, 0, 64), (40, 27, 27, 0, 2, 64),
+    (75, 1, 1, 0, 0, 64), (50, 2, 2, 1, 0, 64), (64, 27, 27, 0, 0, 8), (100, 5, 7, 0, 0, 36), (33, 10, 10, 2, 0, 4),
 ])
-def test_rank1_gemm_kernel(torch, elements, ni, nj, op, offset):
+def test_rank1_gemm_kernel(torch, elements, ni, nj, op, offset, q):
     rng = np.random.default_rng(elements + ni)
-    w = rng.random((elements, 64)) + 0.5
-    b1 = rng.random((64, ni)) * 2 - 1
+    w = rng.random((elements, q)) + 0.5
+    b1 = rng.random((q, ni)) * 2 - 1
     # the same matrix twice selects the symmetric path; offset == 2 forces two distinct square matrices
-    b2 = b1 if (ni == nj and offset != 2) else rng.random((64, nj)) * 2 - 1
+    b2 = b1 if (ni == nj and offset != 2) else rng.random((q, nj)) * 2 - 1
     offset = offset % 2
     m0 = rng.random((elements, ni, nj))
     prod, mags = np.zeros_like(m0), np.zeros_like(m0)
@@ -58,26 +58,28 @@ def test_rank1_gemm_kernel(torch, elements, ni, nj, op, offset):
     keep_1, p1 = to_dev(torch, b1)
     keep_2, p2 = (keep_1, p1) if b2 is b1 else to_dev(torch, b2)
     keep_m, pm = to_dev(torch, m0)
-    assert lib().acro_b200_rank1_gemm_supported(64, ni, nj) == 1
-    check(lib().acro_b200_rank1_gemm(pw, p1, p2, pm, elements, 64, ni, nj, op, None))
+    assert lib().acro_b200_rank1_gemm_supported(q, ni, nj) == 1 and lib().acro_b200_rank1_gemm_supported(q + 1, ni, nj) == 0
+    check(lib().acro_b200_rank1_gemm(pw, p1, p2, pm, elements, q, ni, nj, op, None))
     status_ok()
     got = keep_m.cpu().numpy().reshape(m0.shape)
     assert oracle.parity_error(got, expect, mags + np.abs(m0)) <= TOL
 
 
-@pytest.mark.parametrize("batch,op,offset", [(1, 0, 0), (2, 1, 0), (5, 2, 0), (3, 0, 1), (500, 0, 0)])
-def test_batched_gemm_kernel(torch, batch, op, offset):
+@pytest.mark.parametrize("batch,op,offset,n", [(1, 0, 0, 64), (2, 1, 0, 64), (5, 2, 0, 64), (3, 0, 1, 64), (500, 0, 0, 64),
+                                                 (1, 0, 0, 32), (7, 1, 1, 32), (3000, 0, 0, 32)])
+def test_batched_gemm_kernel(torch, batch, op, offset, n):
     rng = np.random.default_rng(batch)
-    a, b = rng.standard_normal((batch, 64, 64)), rng.standard_normal((batch, 64, 64))
-    c0 = rng.random((batch, 64, 64))
+    a, b = rng.standard_normal((batch, n, n)), rng.standard_normal((batch, n, n))
+    c0 = rng.random((batch, n, n))
     ka, pa = to_dev(torch, a, offset)
     kb, pb = to_dev(torch, b)
     kc, pc = to_dev(torch, c0)
-    check(lib().acro_b200_batched_gemm(pa, pb, pc, batch, 64, 64, 64, op, None))
+    assert lib().acro_b200_batched_gemm_supported(n, n, n) == 1 and lib().acro_b200_batched_gemm_supported(n, n, 16) == 0
+    check(lib().acro_b200_batched_gemm(pa, pb, pc, batch, n, n, n, op, None))
     status_ok()
     got = kc.cpu().numpy().reshape(c0.shape)
     sample = sorted(set([0, batch // 2, batch - 1]))         # the oracle needs 262144 terms per matrix
-    prod = np.zeros((len(sample), 64, 64))
+    prod = np.zeros((len(sample), n, n))
     mags = np.zeros_like(prod)
     oracle.contract("port", "C_e_i_j = A_e_i_k B_e_k_j", prod, a[sample], b[sample])
     oracle.contract("port", "C_e_i_j = A_e_i_k B_e_k_j", mags, np.abs(a[sample]), np.abs(b[sample]))
@@ -90,29 +92,31 @@ def test_batched_gemm_kernel(torch, batch, op, offset):
 
 
 def run_chain_oracle(b, u, w):
-    e = u.shape[0]
-    t = {"B": b, "U": u, "W": w, "T1": np.zeros((e, 4, 4, 5)), "T2": np.zeros((e, 4, 5, 5)), "X": np.zeros((e, 5, 5, 5)),
-         "Y1": np.zeros((e, 4, 5, 5)), "Y2": np.zeros((e, 4, 4, 5)), "V": np.zeros((e, 4, 4, 4))}
+    e, p, q = u.shape[0], u.shape[1], w.shape[1]
+    t = {"B": b, "U": u, "W": w, "T1": np.zeros((e, p, p, q)), "T2": np.zeros((e, p, q, q)), "X": np.zeros((e, q, q, q)),
+         "Y1": np.zeros((e, p, q, q)), "Y2": np.zeros((e, p, p, q)), "V": np.zeros((e, p, p, p))}
     names = sorted(t)
     prog = [(k, names.index(o), [names.index(i) for i in ins]) for k, o, ins in MASS_CHAIN]
     oracle.run("port", [t[n] for n in names], prog, multi=True)
     return t["V"]
 
 
-@pytest.mark.parametrize("elements,offset", [(1, 0), (31, 0), (32, 0), (33, 0), (1000, 0), (65, 1), (10007, 0)])
-def test_sumfact_mass_kernel(torch, elements, offset):
+@pytest.mark.parametrize("elements,offset,p", [(1, 0, 4), (31, 0, 4), (32, 0, 4), (33, 0, 4), (1000, 0, 4), (65, 1, 4), (10007, 0, 4),
+                                                (1, 0, 3), (100, 0, 3), (5001, 1, 3), (33, 0, 2), (20000, 0, 2), (77, 1, 2)])
+def test_sumfact_mass_kernel(torch, elements, offset, p):
     rng = np.random.default_rng(elements)
-    b = rng.random((5, 4)) * 2 - 1
-    u = rng.random((elements, 4, 4, 4)) * 2 - 1
-    w = rng.random((elements, 5, 5, 5)) + 0.5
+    q = p + 1
+    b = rng.random((q, p)) * 2 - 1
+    u = rng.random((elements, p, p, p)) * 2 - 1
+    w = rng.random((elements, q, q, q)) + 0.5
     ref = run_chain_oracle(b, u, w)
     mags = run_chain_oracle(np.abs(b), np.abs(u), w)
     kb, pb = to_dev(torch, b)
     ku, pu = to_dev(torch, u, offset)
     kw, pw = to_dev(torch, w)
     kv, pv = to_dev(torch, np.full(ref.shape, -1.0))
-    assert lib().acro_b200_sumfact_mass_supported(4, 5) == 1 and lib().acro_b200_sumfact_mass_supported(3, 4) == 0
-    check(lib().acro_b200_sumfact_mass(pb, pu, pw, pv, elements, 4, 5, None))
+    assert lib().acro_b200_sumfact_mass_supported(p, q) == 1 and lib().acro_b200_sumfact_mass_supported(5, 6) == 0
+    check(lib().acro_b200_sumfact_mass(pb, pu, pw, pv, elements, p, q, None))
     status_ok()
     got = kv.cpu().numpy().reshape(ref.shape)
     assert oracle.parity_error(got, ref, mags) <= TOL
