@@ -237,10 +237,12 @@ __host__ __device__ inline SymLayout sym_layout(int ni, int tile_e, int images)
     return l;
 }
 
-template <class C>
+// QC: the contracted extent when known at compile time (64), 0 = taken from the arguments.
+template <class C, int QC>
 __global__ void __launch_bounds__(C::THREADS, C::CTAS)
 rank1_gemm_sym_kernel(const Rank1Args a)
 {
+    const int q_ext = QC > 0 ? QC : a.q;
     constexpr int NTW = C::NTW, MT = C::MT, TE = C::TILE_E, THREADS = C::THREADS;
     extern __shared__ __align__(128) unsigned char raw[];
     const int ni = a.ni, nc = ni * ni, n_cols = ni * (ni + 1) / 2;
@@ -339,7 +341,7 @@ rank1_gemm_sym_kernel(const Rank1Args a)
 #pragma unroll
             for (int nt = 0; nt < NTW; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
 #pragma unroll 2
-        for (int k0 = 0; k0 < a.q; k0 += 4)
+        for (int k0 = 0; k0 < q_ext; k0 += 4)
         {
             double af[MT], bf[NTW];
 #pragma unroll
@@ -433,7 +435,7 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
     if (symmetric)
     {
         const SymLayout L = sym_layout(ni, SymSmall::TILE_E, SymSmall::IMAGES);
-        auto sym_kernel = rank1_gemm_sym_kernel<SymSmall>;
+        auto sym_kernel = q == QN ? rank1_gemm_sym_kernel<SymSmall, QN> : rank1_gemm_sym_kernel<SymSmall, 0>;
         cudaError_t st = cudaFuncSetAttribute(sym_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
         if (st != cudaSuccess) return fail_cuda(st, "acro_b200_rank1_gemm (shared memory opt-in)");
         const int64_t sym_tiles = (elements + SymSmall::TILE_E - 1) / SymSmall::TILE_E;
