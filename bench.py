@@ -501,36 +501,51 @@ def run_ops(args):
 
 # ----------------------------------------------------------------------------- CPU arms
 
-def cpu_time_workload(w, batch, threads, seed=0):
-    """Seconds the reference CPU executor needs for `batch` units of workload w."""
-    from oracle import oracle
-    from acrotensor_b200.runner import alloc_host
-    host = alloc_host(w, batch, w.make_inputs(batch, seed=seed))
-    names = sorted(host)
-    prog = [(k, names.index(o), [names.index(i) for i in ins]) for k, o, ins in w.program]
-    arrays = [host[n] for n in names]
+class CpuSample:
+    """A bounded sample of every selected workload for the reference CPU executor: seeded host
+    inputs for a leading slab of the batch, generated once and reused by every pass."""
+
+    def __init__(self, workloads, args, sample_scale):
+        from acrotensor_b200.runner import alloc_host
+        self.items = []
+        for w in workloads:
+            full = max(1, int(round(w.batch * args.scale)))
+            sample = max(1, min(full, int(CPU_SAMPLE[w.key] * sample_scale)))
+            host = alloc_host(w, sample, w.make_inputs(sample, seed=args.seed))
+            names = sorted(host)
+            prog = [(k, names.index(o), [names.index(i) for i in ins]) for k, o, ins in w.program]
+            self.items.append((w, full, sample, [host[n] for n in names], prog, [w.batched(n) for n in names]))
+
+    def run(self, threads):
+        """One pass.  Returns (suite GB/s extrapolated to the full batches, extrapolated seconds,
+        per-configuration detail, 'reference' | 'port')."""
+        from oracle import oracle
+        full_seconds, detail, total_bytes = 0.0, {}, 0
+        kind = "reference" if oracle.have("ref") else "port"
+        for w, full, sample, arrays, prog, batched in self.items:
+            t0 = time.perf_counter()
+            if kind == "reference":
+                oracle.run_ref_slabs(arrays, prog, batched, sample, threads, multi=w.multi)
+            else:
+                oracle.run("port", arrays, prog, multi=w.multi)
+            sec = time.perf_counter() - t0
+            # the interpreted executor's cost is linear in the batch
+            full_s = sec * (full / sample)
+            full_seconds += full_s
+            total_bytes += w.bytes(full)
+            detail[w.key] = {"sample_batch": sample, "sample_s": round(sec, 3), "full_s_extrapolated": round(full_s, 2)}
+        return total_bytes / full_seconds * 1e-9, full_seconds, detail, kind
+
+
+def cpu_sample_for_budget(workloads, args, threads, seconds_per_pass):
+    """Calibrates on a small sample, then sizes the sample so that one pass takes about
+    `seconds_per_pass` on this machine."""
+    small = CpuSample(workloads, args, 0.25)
     t0 = time.perf_counter()
-    if oracle.have("ref"):
-        oracle.run_ref_slabs(arrays, prog, [w.batched(n) for n in names], batch, threads, multi=w.multi)
-        kind = "reference"
-    else:
-        oracle.run("port", arrays, prog, multi=w.multi)
-        kind = "port"
-    return time.perf_counter() - t0, kind
-
-
-def cpu_suite(workloads, args, threads, sample_scale):
-    """Runs a bounded sample of every workload and extrapolates to the full batch (the
-    interpreted executor's cost is linear in the batch)."""
-    full_seconds, detail, kind = 0.0, {}, "port"
-    for w in workloads:
-        sample = max(1, min(int(w.batch * args.scale), int(CPU_SAMPLE[w.key] * sample_scale)))
-        sec, kind = cpu_time_workload(w, sample, threads, seed=args.seed)
-        full = sec * (max(1, int(round(w.batch * args.scale))) / sample)
-        full_seconds += full
-        detail[w.key] = {"sample_batch": sample, "sample_s": round(sec, 3), "full_s_extrapolated": round(full, 2)}
-    total_bytes = sum(w.bytes(max(1, int(round(w.batch * args.scale)))) for w in workloads)
-    return total_bytes / full_seconds * 1e-9, full_seconds, detail, kind
+    small.run(threads)
+    took = max(time.perf_counter() - t0, 1e-3)
+    scale = 0.25 * seconds_per_pass / took
+    return CpuSample(workloads, args, max(0.05, scale))
 
 
 def host_threads():
@@ -544,7 +559,8 @@ def host_threads():
 def cpu_baseline(workloads, args):
     from oracle import oracle
     threads = host_threads() if oracle.have("ref") else 1
-    gbs, full_s, detail, kind = cpu_suite(workloads, args, threads, sample_scale=max(1.0, threads / 4.0))
+    sample = cpu_sample_for_budget(workloads, args, threads, 10.0)
+    gbs, full_s, detail, kind = sample.run(threads)
     return {"value": round(gbs, 4), "unit": "GB/s", "cores": threads, "kind": kind,
             "sample": "per configuration a leading slab of the batch (sizes in detail), time scaled linearly to the full batch",
             "full_suite_seconds_extrapolated": round(full_s, 1), "detail": detail}
@@ -559,13 +575,15 @@ def run_reference(args):
         oracle.build()
     workloads = selected(args.workload)
     threads = host_threads() if oracle.have("ref") else 1
-    sample_scale = max(1.0, threads / 4.0)
+    # every pass is a bounded sample; the whole run stays within a few minutes
+    per_pass = max(0.5, min(8.0, 150.0 / (args.steps + args.warmup)))
+    sample = cpu_sample_for_budget(workloads, args, threads, per_pass)
     for _ in range(args.warmup):
-        cpu_suite(workloads, args, threads, sample_scale * 0.25)
+        sample.run(threads)
     vals, secs = [], []
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        gbs, full_s, detail, kind = cpu_suite(workloads, args, threads, sample_scale)
+        gbs, full_s, detail, kind = sample.run(threads)
         vals.append(gbs)
         secs.append(full_s)
     wall = time.perf_counter() - t0
@@ -589,7 +607,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="suite", choices=["suite", "cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "ops"])
