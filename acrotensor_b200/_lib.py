@@ -46,7 +46,8 @@ class GenericDesc(ctypes.Structure):
 class PointwiseDesc(ctypes.Structure):
     _fields_ = [("dim", ctypes.c_int32), ("op", ctypes.c_int32), ("n_point_loops", ctypes.c_int32),
                 ("n_scalars", ctypes.c_int32), ("point_extent", ctypes.c_int64 * MAX_POINT_LOOPS),
-                ("scalar_step", (ctypes.c_int64 * MAX_POINT_LOOPS) * MAX_SCALARS)]
+                ("scalar_step", (ctypes.c_int64 * MAX_POINT_LOOPS) * MAX_SCALARS),
+                ("cell_points", ctypes.c_int64), ("swapped", ctypes.c_int32), ("reserved", ctypes.c_int32)]
 
 
 _P = ctypes.c_void_p

@@ -173,7 +173,10 @@ bool plan_reduce_batch(DimensionedKernel &k, int ki, Step &s)
 }
 
 // ---------------------------------------------------------------- pointwise_sym
-// D_P_m_n = (scalars over P, left to right) X_P_m_l Y_P_n_l, the scalars first in the string.
+// D_<lead>_m_n_<trail> = (factors over the points, left to right) X_<lead>_<trail>_a_l Y_<lead>_<trail>_b_l
+// with {a, b} = {m, n}, the factors first in the string.  <trail> empty is the point-major
+// layout (D_e_k_m_n); a non-empty <trail> is the cell-major layout of the reference's own
+// partial-assembly tests (D_e_m_n_k1_k2_k3).
 bool plan_pointwise_sym(DimensionedKernel &k, int ki, Step &s)
 {
     const Names out = k.OutputVar.IndexNames;
@@ -181,16 +184,21 @@ bool plan_pointwise_sym(DimensionedKernel &k, int ki, Step &s)
     const int nin = k.GetNumInputVars();
     if (nin < 2 || nin - 2 > ACRO_B200_MAX_SCALARS) return false;
     const std::string l = k.ContractionIndexNames[0];
-    const std::string m = out[out.size() - 2], n = out[out.size() - 1];
-    const Names P(out.begin(), out.end() - 2);
-    if (P.size() > ACRO_B200_MAX_POINT_LOOPS) return false;
-    const std::int64_t dim = extent_of(k, m);
-    if (extent_of(k, n) != dim || extent_of(k, l) != dim) return false;
-
-    Names xs = P, ys = P;
-    xs.push_back(m); xs.push_back(l);
-    ys.push_back(n); ys.push_back(l);
-    if (indices_of(k, nin - 2) != xs || indices_of(k, nin - 1) != ys) return false;
+    const Names xs = indices_of(k, nin - 2), ys = indices_of(k, nin - 1);
+    if (xs.size() < 3 || xs.size() != ys.size() || xs.back() != l || ys.back() != l) return false;
+    const Names P(xs.begin(), xs.end() - 2);            // the point loops, in operand order
+    if (Names(ys.begin(), ys.end() - 2) != P || P.empty() || P.size() > ACRO_B200_MAX_POINT_LOOPS || !distinct(P)) return false;
+    const std::string a = xs[xs.size() - 2], b = ys[ys.size() - 2];
+    if (a == b || a == l || b == l) return false;
+    // m, n adjacent in the output; what precedes and follows them must spell P
+    std::size_t pos = 0;
+    while (pos + 1 < out.size() && !((out[pos] == a && out[pos + 1] == b) || (out[pos] == b && out[pos + 1] == a))) ++pos;
+    if (pos + 1 >= out.size()) return false;
+    const Names lead(out.begin(), out.begin() + pos), trail(out.begin() + pos + 2, out.end());
+    if (concat(lead, trail) != P) return false;
+    const bool swapped = (out[pos] == b);               // the first block operand carries n
+    const std::int64_t dim = extent_of(k, a);
+    if (extent_of(k, b) != dim || extent_of(k, l) != dim) return false;
 
     s = Step();
     acro_b200_pointwise_desc &d = s.pointwise;
@@ -199,6 +207,9 @@ bool plan_pointwise_sym(DimensionedKernel &k, int ki, Step &s)
     d.op = op_code(k);
     d.n_point_loops = static_cast<int>(P.size());
     d.n_scalars = nin - 2;
+    d.swapped = swapped ? 1 : 0;
+    d.cell_points = 1;
+    for (const std::string &idx : trail) d.cell_points *= extent_of(k, idx);
     std::int64_t points = 1;
     for (std::size_t j = 0; j < P.size(); ++j)
     {
@@ -237,8 +248,9 @@ bool plan_pointwise_sym(DimensionedKernel &k, int ki, Step &s)
     s.bytes = 8 * (points * dim * dim * ((same_xy ? 1 : 2) + (s.op == ACRO_B200_OP_ASSIGN ? 1 : 2)) + scalar_entries);
     s.flops = points * dim * dim * dim * (nin);   // (nin-1) multiplies + 1 add per term
     std::ostringstream note;
-    note << points << " points, " << dim << "x" << dim << " block per point, " << d.n_scalars
-         << " point-wise factors; tiles staged through shared memory";
+    note << points << " points, " << dim << "x" << dim << " block per point, " << d.n_scalars << " point-wise factors, "
+         << (d.cell_points > 1 ? "cell-major output (" + std::to_string(d.cell_points) + " points per cell)" : std::string("point-major output"))
+         << (swapped ? ", block transposed" : "") << "; tiles through a ring of asynchronous bulk copies";
     s.note = note.str();
     return true;
 }

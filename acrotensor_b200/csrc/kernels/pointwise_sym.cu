@@ -281,9 +281,216 @@ int launch_pipe(const PointwiseArgs &args, cudaStream_t s, int ctas_per_sm)
     return launch_status("acro_b200_pointwise_sym (pipelined)");
 }
 
+
+// ------------------------------------------------------------------ cell-major output
+// D[cell][m][n][k]: the K points of a cell come after the block indices.  Block (a,b) of a
+// point, blk[a][b] = sum_l (s X[a][l]) Y[b][l], lands at (m,n) = (a,b), or (b,a) when the
+// string lists the n-operand first.
+
+template <int DIM>
+__device__ __forceinline__ void point_block(const PointwiseArgs &a, double s, const double *x, const double *y, double *blk)
+{
+#pragma unroll
+    for (int p = 0; p < DIM; ++p)
+    {
+        double sx[DIM];
+#pragma unroll
+        for (int l = 0; l < DIM; ++l) sx[l] = (a.d.n_scalars > 0) ? __dmul_rn(s, x[p * DIM + l]) : x[p * DIM + l];
+#pragma unroll
+        for (int q = 0; q < DIM; ++q)
+        {
+            double acc = 0.0;
+#pragma unroll
+            for (int l = 0; l < DIM; ++l) acc = __dadd_rn(acc, __dmul_rn(sx[l], y[q * DIM + l]));
+            blk[p * DIM + q] = acc;
+        }
+    }
+}
+
+// Direct kernel: one thread per point, operands straight from global memory.  Consecutive
+// threads are consecutive points of a cell, so each of the dim*dim stores is coalesced.
+// Serves "+=" / "-=", unaligned operands and the ragged tail of the pipelined kernel.
+template <int DIM>
+__global__ void __launch_bounds__(kTile)
+pointwise_cell_direct_kernel(const __grid_constant__ PointwiseArgs a)
+{
+    constexpr int BLK = DIM * DIM;
+    const int64_t K = a.d.cell_points;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kTile;
+    for (int64_t p = static_cast<int64_t>(blockIdx.x) * kTile + threadIdx.x; p < a.points; p += stride)
+    {
+        const int64_t gp = a.first_point + p;
+        const double s = a.d.n_scalars > 0 ? scalar_product(a, gp) : 1.0;
+        double x[BLK], y[BLK], blk[BLK];
+#pragma unroll
+        for (int i = 0; i < BLK; ++i)
+        {
+            x[i] = a.X[p * BLK + i];
+            y[i] = a.Y[p * BLK + i];
+        }
+        point_block<DIM>(a, s, x, y, blk);
+        double *cell = a.D + (p / K) * BLK * K + (p % K);
+#pragma unroll
+        for (int i = 0; i < BLK; ++i)
+        {
+            const int pos = a.d.swapped ? (i % DIM) * DIM + i / DIM : i;
+            double *dst = cell + pos * K;
+            if (a.d.op == ACRO_B200_OP_ASSIGN) *dst = blk[i];
+            else if (a.d.op == ACRO_B200_OP_ADD) *dst = __dadd_rn(*dst, blk[i]);
+            else *dst = __dsub_rn(*dst, blk[i]);
+        }
+    }
+}
+
+// Pipelined kernel for "=": tiles of whole cells (tile_pts points, a multiple of K, at most
+// kTile) through the same ring of bulk copies as the point-major kernel.  The result is
+// written back into the tile buffer in cell-major order, which is not the thread's own slots,
+// hence one more CTA barrier between reading the operands and writing the results.
+template <int DIM, bool SAME_XY, int STAGES>
+__global__ void __launch_bounds__(kTile)
+pointwise_cell_pipe_kernel(const __grid_constant__ PointwiseArgs a, int tile_pts)
+{
+    constexpr int BLK = DIM * DIM;
+    constexpr int SLOT = kTile * BLK;                    // doubles reserved per ring slot
+    extern __shared__ __align__(128) double smem[];
+    double *bx = smem;
+    double *by = smem + (SAME_XY ? 0 : STAGES * SLOT);
+    __shared__ uint64_t full[STAGES];
+
+    const int tid = threadIdx.x;
+    const int K = static_cast<int>(a.d.cell_points);
+    const int tile_doubles = tile_pts * BLK;
+    const uint32_t tile_bytes = static_cast<uint32_t>(tile_doubles) * 8u;
+    const int64_t n_full = a.points / tile_pts;
+    if (tid == 0)
+    {
+        for (int i = 0; i < STAGES; ++i) mbar_init(&full[i], 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    auto load_tile = [&](int64_t tile, int st) {
+        mbar_arrive_expect_tx(&full[st], SAME_XY ? tile_bytes : 2 * tile_bytes);
+        bulk_load(bx + st * SLOT, a.X + tile * tile_doubles, tile_bytes, &full[st]);
+        if (!SAME_XY) bulk_load(by + st * SLOT, a.Y + tile * tile_doubles, tile_bytes, &full[st]);
+    };
+    if (tid == 0)
+    {
+        for (int j = 0; j < STAGES - 1; ++j)
+        {
+            const int64_t tile = blockIdx.x + static_cast<int64_t>(j) * gridDim.x;
+            if (tile < n_full) load_tile(tile, j);
+        }
+    }
+
+    const bool active = tid < tile_pts;
+    const int cell = tid / K, k = tid % K;
+    int64_t i = 0;
+    for (int64_t tile = blockIdx.x; tile < n_full; tile += gridDim.x, ++i)
+    {
+        const int st = static_cast<int>(i % STAGES);
+        const double s = (active && a.d.n_scalars > 0) ? scalar_product(a, a.first_point + tile * tile_pts + tid) : 1.0;
+        if (!mbar_wait(&full[st], static_cast<uint32_t>((i / STAGES) & 1))) atomicExch(a.wait_flag, 1);
+
+        double x[BLK], y[BLK], blk[BLK];
+        if (active)
+        {
+#pragma unroll
+            for (int j = 0; j < BLK; ++j)
+            {
+                x[j] = bx[st * SLOT + tid * BLK + j];
+                y[j] = SAME_XY ? x[j] : by[st * SLOT + tid * BLK + j];
+            }
+            point_block<DIM>(a, s, x, y, blk);
+        }
+        __syncthreads();         // every operand of the tile is in registers
+        if (active)
+        {
+            double *out = bx + st * SLOT + cell * BLK * K + k;
+#pragma unroll
+            for (int j = 0; j < BLK; ++j)
+            {
+                const int pos = a.d.swapped ? (j % DIM) * DIM + j / DIM : j;
+                out[pos * K] = blk[j];
+            }
+        }
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0)
+        {
+            bulk_store(a.D + tile * tile_doubles, bx + st * SLOT, tile_bytes);
+            bulk_commit();
+            const int64_t next = tile + static_cast<int64_t>(STAGES - 1) * gridDim.x;
+            if (next < n_full)
+            {
+                bulk_wait_read<1>();
+                load_tile(next, static_cast<int>((i + STAGES - 1) % STAGES));
+            }
+        }
+    }
+    if (tid == 0) bulk_wait_all<0>();
+}
+
+template <int DIM>
+int launch_cell(const PointwiseArgs &args_in, cudaStream_t s)
+{
+    constexpr int BLK = DIM * DIM;
+    PointwiseArgs args = args_in;
+    const int64_t K = args.d.cell_points;
+    const int tile_pts = K <= kTile ? static_cast<int>((kTile / K) * K) : 0;
+    const bool pipe = args.d.op == ACRO_B200_OP_ASSIGN && tile_pts > 0 && (tile_pts * BLK) % 2 == 0 && args.points >= tile_pts &&
+                      aligned16(args.X) && aligned16(args.Y) && aligned16(args.D);
+    if (pipe)
+    {
+        const bool same_xy = args.X == args.Y;
+        const int stages = (DIM == 3 && !same_xy) ? 3 : 4;
+        const size_t smem = static_cast<size_t>(stages) * kTile * BLK * sizeof(double) * (same_xy ? 1 : 2);
+        const int64_t n_full = args.points / tile_pts;
+        int64_t grid = static_cast<int64_t>(sm_count()) * (DIM == 3 ? (same_xy ? 3 : 2) : 4);
+        if (grid > n_full) grid = n_full;
+        cudaError_t status;
+        if (same_xy)
+        {
+            auto kernel = pointwise_cell_pipe_kernel<DIM, true, 4>;
+            status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (status != cudaSuccess) return fail_cuda(status, "acro_b200_pointwise_sym (shared memory opt-in)");
+            kernel<<<static_cast<int>(grid), kTile, smem, s>>>(args, tile_pts);
+        }
+        else if (DIM == 3)
+        {
+            auto kernel = pointwise_cell_pipe_kernel<DIM, false, 3>;
+            status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (status != cudaSuccess) return fail_cuda(status, "acro_b200_pointwise_sym (shared memory opt-in)");
+            kernel<<<static_cast<int>(grid), kTile, smem, s>>>(args, tile_pts);
+        }
+        else
+        {
+            auto kernel = pointwise_cell_pipe_kernel<DIM, false, 4>;
+            status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (status != cudaSuccess) return fail_cuda(status, "acro_b200_pointwise_sym (shared memory opt-in)");
+            kernel<<<static_cast<int>(grid), kTile, smem, s>>>(args, tile_pts);
+        }
+        const int rc = launch_status("acro_b200_pointwise_sym (cell-major, pipelined)");
+        if (rc != ACRO_B200_OK) return rc;
+        const int64_t done = n_full * tile_pts;     // a multiple of K: whole cells
+        if (done == args.points) return ACRO_B200_OK;
+        args.X += done * BLK;
+        args.Y += done * BLK;
+        args.D += done * BLK;
+        args.first_point += done;
+        args.points -= done;
+    }
+    int64_t grid = (args.points + kTile - 1) / kTile;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    if (grid > cap) grid = cap;
+    pointwise_cell_direct_kernel<DIM><<<static_cast<int>(grid), kTile, 0, s>>>(args);
+    return launch_status("acro_b200_pointwise_sym (cell-major)");
+}
+
 template <int DIM>
 int launch(const PointwiseArgs &args_in, cudaStream_t s)
 {
+    if (args_in.d.cell_points > 1 || args_in.d.swapped) return launch_cell<DIM>(args_in, s);
     PointwiseArgs args = args_in;
     // "=" on 16-byte aligned operands: whole tiles through the bulk-copy pipeline, then the
     // ragged tail (if any) through the plain kernel below.
@@ -325,10 +532,14 @@ int acro_b200_pointwise_sym_supported(const acro_b200_pointwise_desc *d)
     if (d->n_point_loops < 1 || d->n_point_loops > ACRO_B200_MAX_POINT_LOOPS) return 0;
     if (d->n_scalars < 0 || d->n_scalars > ACRO_B200_MAX_SCALARS) return 0;
     if (d->op < 0 || d->op > 2) return 0;
+    int64_t points = 1;
     for (int j = 0; j < d->n_point_loops; ++j)
     {
         if (d->point_extent[j] < 1) return 0;
+        points *= d->point_extent[j];
     }
+    if (d->cell_points < 1 || points % d->cell_points != 0) return 0;
+    if (d->swapped != 0 && d->swapped != 1) return 0;
     return 1;
 }
 

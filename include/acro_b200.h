@@ -185,6 +185,16 @@ typedef struct acro_b200_pointwise_desc
     int32_t n_scalars;
     int64_t point_extent[ACRO_B200_MAX_POINT_LOOPS];
     int64_t scalar_step[ACRO_B200_MAX_SCALARS][ACRO_B200_MAX_POINT_LOOPS];
+    /* Output layout.  cell_points = 1: D holds the dim*dim block of each point contiguously
+     * (D_e_k_m_n).  cell_points = K > 1: the last point loops (K points, a "cell") come AFTER
+     * the block indices, D[cell][m][n][k] (D_e_m_n_k1_k2_k3, the layout of the reference's own
+     * partial-assembly tests, unittest/kernel/test_TensorEngine.cpp:498-590); the point
+     * count must be a multiple of K.  X and Y are point-major in both cases. */
+    int64_t cell_points;
+    /* 0: D[m][n] = sum_l (s X[m][l]) Y[n][l];  1: the string lists the n-operand first,
+     * D[m][n] = sum_l (s X[n][l]) Y[m][l] (same values up to rounding, different term order). */
+    int32_t swapped;
+    int32_t reserved;
 } acro_b200_pointwise_desc;
 
 int acro_b200_pointwise_sym_supported(const acro_b200_pointwise_desc *desc);

@@ -98,8 +98,14 @@ def test_family_selection():
     # a tiny reduction stays on the generic kernel (bit-identical to the reference there)
     text = ab.describe_plan(["A_i=B_j_i"], [[(3,), (5, 3)]])
     assert "family=generic" in text
-    # the reference tests' D-tensor layout (m,n before the point indices) is not the pointwise layout
+    # the reference tests' D-tensor layout (m,n before the trailing point indices) is the cell-major pointwise layout
     text = ab.describe_plan(["D_e_m_n_k = W_e_k J_e_k_m_j J_e_k_n_j"], [[(10, 2, 2, 4), (10, 4), (10, 4, 2, 2), (10, 4, 2, 2)]])
+    assert "family=pointwise_sym" in text and "cell-major output (4 points per cell)" in text and "transposed" not in text
+    text = ab.describe_plan(["D_e_m_n_k1_k2 = W_k1_k2 Jd_e_k1_k2 J_e_k1_k2_n_j J_e_k1_k2_m_j"],
+                            [[(10, 3, 3, 5, 5), (5, 5), (10, 5, 5), (10, 5, 5, 3, 3), (10, 5, 5, 3, 3)]])
+    assert "family=pointwise_sym" in text and "25 points per cell" in text and "block transposed" in text
+    # block indices that are not adjacent in the output stay generic
+    text = ab.describe_plan(["D_m_e_n = J_e_m_j J_e_n_j"], [[(2, 10, 2), (10, 2, 2), (10, 2, 2)]])
     assert "family=generic" in text
 
 

@@ -259,6 +259,7 @@ def test_pointwise_sym_kernel(torch, dim, points, same, nscal, op):
 
     desc = _lib.PointwiseDesc()
     desc.dim, desc.op, desc.n_point_loops, desc.n_scalars = dim, op, 2, nscal
+    desc.cell_points = 1
     desc.point_extent[0], desc.point_extent[1] = e, k
     steps = {"_k": (0, 1), "_e_k": (k, 1), "_e": (1, 0)}
     for i, s in enumerate(scal_idx):
@@ -329,6 +330,7 @@ def test_full_size_pointwise_properties(torch):
     d = torch.empty(E, K, 3, 3, dtype=torch.float64, device="cuda")
     desc = _lib.PointwiseDesc()
     desc.dim, desc.op, desc.n_point_loops, desc.n_scalars = 3, 0, 2, 2
+    desc.cell_points = 1
     desc.point_extent[0], desc.point_extent[1] = E, K
     desc.scalar_step[0][0], desc.scalar_step[0][1] = 0, 1
     desc.scalar_step[1][0], desc.scalar_step[1][1] = K, 1
@@ -349,3 +351,38 @@ def test_full_size_pointwise_properties(torch):
     untouched = torch.ones(E, dtype=torch.bool, device="cuda")
     untouched[sample] = False
     assert bool((d[untouched] == expect).all())
+
+
+@pytest.mark.parametrize("cells,kshape,dim,swapped,same,op", [
+    (1001, (64,), 3, False, True, "="), (333, (5, 5, 5), 3, True, True, "="), (70, (4, 4), 2, False, False, "="),
+    (515, (5, 5, 5), 3, True, False, "="), (9, (3, 3, 3), 3, True, True, "+="), (300, (7,), 3, False, True, "="),
+    (1000, (300,), 3, False, True, "="), (64, (2, 2), 1, True, False, "="),
+])
+def test_pointwise_cell_major_layout_through_the_engine(cells, kshape, dim, swapped, same, op):
+    """D_e_m_n_k.. = W_k.. Det_e_k.. X_e_k.._a_l Y_e_k.._b_l : the layout of the reference's own
+    partial-assembly tests (block indices before the trailing point indices)."""
+    rng = np.random.default_rng(cells + dim)
+    kidx = ["k%d" % (i + 1) for i in range(len(kshape))]
+    ks = "_".join(kidx)
+    a, b = ("n", "m") if swapped else ("m", "n")
+    kernel = "D_e_m_n_%s %s W_%s Det_e_%s X_e_%s_%s_l %s_e_%s_%s_l" % (ks, op, ks, ks, ks, a, "X" if same else "Y", ks, b)
+    shape_k = tuple(kshape)
+    w = rng.random(shape_k) + 0.5
+    det = rng.random((cells,) + shape_k) + 0.5
+    x = rng.random((cells,) + shape_k + (dim, dim)) * 2 - 1
+    y = x if same else rng.random((cells,) + shape_k + (dim, dim)) * 2 - 1
+    d0 = rng.random((cells, dim, dim) + shape_k)
+    ref = d0.copy()
+    oracle.contract("port", kernel, ref, w, det, x, y)
+    got = d0.copy()
+    te = ab.TensorEngine("Cuda")
+    D = ab.Tensor(got.shape, hdata=got)
+    X = ab.Tensor(x.shape, hdata=x)
+    Y = X if same else ab.Tensor(y.shape, hdata=y)
+    args = (ab.Tensor(w.shape, hdata=w), ab.Tensor(det.shape, hdata=det), X, Y)
+    plan = te.GetImplementation(kernel, D, *args)
+    assert "family=pointwise_sym" in plan and ("cell-major" in plan or int(np.prod(kshape)) == 1)
+    te(kernel, D, *args)
+    D.MoveFromGPU()
+    assert np.array_equal(got, ref), plan           # same operation order as the reference: bit-identical
+    assert lib().acro_b200_device_status() == _lib.OK
