@@ -287,6 +287,8 @@ int launch_pipe(const PointwiseArgs &args, cudaStream_t s, int ctas_per_sm)
 // point, blk[a][b] = sum_l (s X[a][l]) Y[b][l], lands at (m,n) = (a,b), or (b,a) when the
 // string lists the n-operand first.
 
+// blk holds the starting values on entry (0, or the old output for "+=", whose terms the
+// reference adds one by one onto the existing value) and the sums on return.
 template <int DIM>
 __device__ __forceinline__ void point_block(const PointwiseArgs &a, double s, const double *x, const double *y, double *blk)
 {
@@ -299,7 +301,7 @@ __device__ __forceinline__ void point_block(const PointwiseArgs &a, double s, co
 #pragma unroll
         for (int q = 0; q < DIM; ++q)
         {
-            double acc = 0.0;
+            double acc = blk[p * DIM + q];
 #pragma unroll
             for (int l = 0; l < DIM; ++l) acc = __dadd_rn(acc, __dmul_rn(sx[l], y[q * DIM + l]));
             blk[p * DIM + q] = acc;
@@ -328,16 +330,21 @@ pointwise_cell_direct_kernel(const __grid_constant__ PointwiseArgs a)
             x[i] = a.X[p * BLK + i];
             y[i] = a.Y[p * BLK + i];
         }
-        point_block<DIM>(a, s, x, y, blk);
         double *cell = a.D + (p / K) * BLK * K + (p % K);
 #pragma unroll
         for (int i = 0; i < BLK; ++i)
         {
             const int pos = a.d.swapped ? (i % DIM) * DIM + i / DIM : i;
+            blk[i] = (a.d.op == ACRO_B200_OP_ADD) ? cell[pos * K] : 0.0;
+        }
+        point_block<DIM>(a, s, x, y, blk);
+#pragma unroll
+        for (int i = 0; i < BLK; ++i)
+        {
+            const int pos = a.d.swapped ? (i % DIM) * DIM + i / DIM : i;
             double *dst = cell + pos * K;
-            if (a.d.op == ACRO_B200_OP_ASSIGN) *dst = blk[i];
-            else if (a.d.op == ACRO_B200_OP_ADD) *dst = __dadd_rn(*dst, blk[i]);
-            else *dst = __dsub_rn(*dst, blk[i]);
+            if (a.d.op == ACRO_B200_OP_SUB) *dst = __dsub_rn(*dst, blk[i]);
+            else *dst = blk[i];
         }
     }
 }
@@ -400,6 +407,7 @@ pointwise_cell_pipe_kernel(const __grid_constant__ PointwiseArgs a, int tile_pts
             {
                 x[j] = bx[st * SLOT + tid * BLK + j];
                 y[j] = SAME_XY ? x[j] : by[st * SLOT + tid * BLK + j];
+                blk[j] = 0.0;
             }
             point_block<DIM>(a, s, x, y, blk);
         }
