@@ -203,6 +203,11 @@ def run_ours(args):
     e2e_mode = "all" if (avail is None or need_all < 0.5 * avail) else ("one" if need_one < 0.5 * avail else "skip")
     if args.e2e_mode != "auto":
         e2e_mode = args.e2e_mode
+    if world > 1:
+        # ranks sample the free memory at slightly different times: rank 0 decides for all
+        decided = [e2e_mode, avail]
+        dist.broadcast_object_list(decided, src=0)
+        e2e_mode, avail = decided
 
     def pinned_buffers(w, dev_t):
         """Pinned host arrays for the inputs and results of one workload; inputs filled from the device."""
@@ -323,6 +328,7 @@ def run_ours(args):
             f.result()
 
     def timed_e2e(order):
+        barrier()      # rank 0 comes late from the spot check; the fused all-reduce waits only about a second for a peer
         e2e_step(order)
         barrier()
         w0 = time.perf_counter()
@@ -352,11 +358,20 @@ def run_ours(args):
     else:
         e2e_ms = float("nan")
 
-    times = torch.tensor([total_ms, e2e_ms] + per_cfg_ms, dtype=torch.float64, device=dev)
+    # a bounded device-side wait that gave up on ANY rank invalidates the whole run: no line is printed
+    status = ab.lib().acro_b200_device_status()
+    status_text = ab.lib().acro_b200_last_error().decode() if status != 0 else ""
+    times = torch.tensor([total_ms, e2e_ms] + per_cfg_ms + [float(-status)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     times = times.tolist()
-    total_ms, e2e_ms, per_cfg_ms = times[0], times[1], times[2:]
+    total_ms, e2e_ms, per_cfg_ms, worst_status = times[0], times[1], times[2:-1], int(times[-1])
+    if worst_status != 0:
+        pool.shutdown()
+        if world > 1:
+            dist.destroy_process_group()
+        raise SystemExit("rank %d: device status %d on this rank, %d on the worst rank: %s"
+                         % (rank, status, -worst_status, status_text or "another rank's launch gave up waiting"))
 
     if rank == 0:
         hbm_peak, peak_kind = measured_peaks()
@@ -421,9 +436,6 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_baseline(workloads, args)
         print(json.dumps(line))
     pool.shutdown()
-    status = ab.lib().acro_b200_device_status()
-    if status != 0:
-        raise SystemExit("device status %d after the run: %s" % (status, ab.lib().acro_b200_last_error().decode()))
     if world > 1:
         dist.destroy_process_group()
 
