@@ -118,7 +118,17 @@ Step plan_generic(DimensionedKernel &k, int ki)
     s.flops = outer_points * terms * k.GetNumInputVars();   // (n_in - 1) multiplies + 1 add per term
     std::ostringstream note;
     if (acro_b200_generic_uses_wide_kernel(&g)) note << "CTA per range of terms (fixed-order tree sum): " << outer_points << " entries x " << terms << " terms";
-    else note << "thread per output entry: " << outer_points << " entries x " << terms << " terms";
+    else
+    {
+        int blocked_loop = -1;
+        const int per_thread = acro_b200_generic_blocking(&g, &blocked_loop);
+        if (per_thread > 1)
+        {
+            note << "thread per " << per_thread << " output entries along " << loops[blocked_loop] << ": " << outer_points
+                 << " entries x " << terms << " terms";
+        }
+        else note << "thread per output entry: " << outer_points << " entries x " << terms << " terms";
+    }
     s.note = note.str();
     return s;
 }

@@ -1,6 +1,7 @@
 // Generic contraction kernel: one thread per output entry, contracted loops run
 // serially in the reference's summation order, without fused multiply-add.
 #include "common.cuh"
+#include <cstring>
 
 using namespace acro_b200_detail;
 
@@ -158,6 +159,229 @@ generic_contract_kernel(const __grid_constant__ acro_b200_generic_desc d, double
     }
 }
 
+// Register-blocked variant: one thread owns R output entries that differ only in one outer
+// index (entry r sits r * (extent / R) steps along that loop, so neighbouring lanes still touch
+// neighbouring addresses).  An input that does not carry the blocked index is loaded once and
+// used for all R entries; the leading inputs that do not carry the innermost contracted index
+// are multiplied once per pass of that loop.  Every entry still sees the reference's
+// left-to-right products and sequential sum, without fused multiply-add: results are
+// bit-identical to the thread-per-entry kernel.  32-bit offsets throughout (the launcher checks).
+constexpr int kBlockedMaxInputs = 5;
+
+struct BlockedArgs
+{
+    int n_outer, n_loops, op;
+    int hoist;                 // leading inputs without the innermost contracted index
+    unsigned int dep_mask;     // bit v: input v carries the blocked index
+    int mid_terms;             // product of the contracted extents but the innermost
+    int blk_out;               // offset between a thread's consecutive entries
+    int blk_in[kBlockedMaxInputs];
+    int extent[ACRO_B200_MAX_LOOPS];      // blocked loop already divided by R
+    int out_step[ACRO_B200_MAX_LOOPS];
+    int in_step[kBlockedMaxInputs][ACRO_B200_MAX_LOOPS];
+};
+
+template <int N_IN, int R>
+__global__ void __launch_bounds__(256)
+generic_blocked_kernel(const __grid_constant__ BlockedArgs a, double *__restrict__ out,
+                       const __grid_constant__ InputPointers ins, unsigned int coarse_points)
+{
+    const unsigned int stride = gridDim.x * blockDim.x;
+    const int n_outer = a.n_outer;
+    const int n_contr = a.n_loops - n_outer;
+    const int inner = a.n_loops - 1;
+    const int e_in = n_contr > 0 ? a.extent[inner] : 1;
+    const int hoist = n_contr > 0 ? a.hoist : 0;
+
+    for (unsigned int point = blockIdx.x * blockDim.x + threadIdx.x; point < coarse_points; point += stride)
+    {
+        int out_off = 0;
+        int off[N_IN];
+#pragma unroll
+        for (int v = 0; v < N_IN; ++v) off[v] = 0;
+        unsigned int rest = point;
+        for (int l = n_outer - 1; l >= 0; --l)
+        {
+            const unsigned int ext = static_cast<unsigned int>(a.extent[l]);
+            const unsigned int q = rest / ext;
+            const int idx = static_cast<int>(rest - q * ext);
+            rest = q;
+            out_off += idx * a.out_step[l];
+#pragma unroll
+            for (int v = 0; v < N_IN; ++v) off[v] += idx * a.in_step[v][l];
+        }
+
+        double acc[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = (a.op == ACRO_B200_OP_ADD) ? out[out_off + r * a.blk_out] : 0.0;
+
+        int counter[ACRO_B200_MAX_LOOPS];
+        for (int c = 0; c < n_contr - 1; ++c) counter[c] = 0;
+
+        for (int mid = 0; mid < a.mid_terms; ++mid)
+        {
+            // product of the leading inputs that stay fixed while the innermost contracted index runs
+            double pre[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) pre[r] = 0.0;
+#pragma unroll
+            for (int v = 0; v < N_IN; ++v)
+            {
+                if (v < hoist)
+                {
+                    if ((a.dep_mask >> v) & 1u)
+                    {
+#pragma unroll
+                        for (int r = 0; r < R; ++r)
+                        {
+                            const double x = ins.p[v][off[v] + r * a.blk_in[v]];
+                            pre[r] = (v == 0) ? x : __dmul_rn(pre[r], x);
+                        }
+                    }
+                    else
+                    {
+                        const double x = ins.p[v][off[v]];
+#pragma unroll
+                        for (int r = 0; r < R; ++r) pre[r] = (v == 0) ? x : __dmul_rn(pre[r], x);
+                    }
+                }
+            }
+
+            int o[N_IN];
+#pragma unroll
+            for (int v = 0; v < N_IN; ++v) o[v] = off[v];
+            for (int i = 0; i < e_in; ++i)
+            {
+                double prod[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) prod[r] = pre[r];
+#pragma unroll
+                for (int v = 0; v < N_IN; ++v)
+                {
+                    if (v >= hoist)
+                    {
+                        if ((a.dep_mask >> v) & 1u)
+                        {
+#pragma unroll
+                            for (int r = 0; r < R; ++r)
+                            {
+                                const double x = ins.p[v][o[v] + r * a.blk_in[v]];
+                                prod[r] = (v == 0) ? x : __dmul_rn(prod[r], x);
+                            }
+                        }
+                        else
+                        {
+                            const double x = ins.p[v][o[v]];
+#pragma unroll
+                            for (int r = 0; r < R; ++r) prod[r] = (v == 0) ? x : __dmul_rn(prod[r], x);
+                        }
+                        if (n_contr > 0) o[v] += a.in_step[v][inner];
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < R; ++r) acc[r] = __dadd_rn(acc[r], prod[r]);
+            }
+
+            // next combination of the other contracted indices (innermost of them fastest)
+            for (int c = n_contr - 2; c >= 0; --c)
+            {
+                const int l = n_outer + c;
+                if (++counter[c] < a.extent[l])
+                {
+#pragma unroll
+                    for (int v = 0; v < N_IN; ++v) off[v] += a.in_step[v][l];
+                    break;
+                }
+                counter[c] = 0;
+#pragma unroll
+                for (int v = 0; v < N_IN; ++v) off[v] -= (a.extent[l] - 1) * a.in_step[v][l];
+            }
+        }
+
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+        {
+            double *dst = out + out_off + r * a.blk_out;
+            *dst = (a.op == ACRO_B200_OP_SUB) ? __dsub_rn(*dst, acc[r]) : acc[r];
+        }
+    }
+}
+
+// Picks the outer loop to block and the entries per thread.  entries = 1: leave the launch to
+// the thread-per-entry kernel.
+struct BlockedPlan
+{
+    int loop = -1;
+    int entries = 1;
+};
+
+BlockedPlan blocked_plan(const acro_b200_generic_desc &d)
+{
+    BlockedPlan p;
+    const int n_contr = d.n_loops - d.n_outer;
+    if (d.n_inputs < 2 || d.n_inputs > kBlockedMaxInputs || n_contr < 1) return p;
+    int64_t outer_points = 1, terms = 1;
+    for (int l = 0; l < d.n_loops; ++l) (l < d.n_outer ? outer_points : terms) *= d.extent[l];
+    if (terms >= 0x7fffffffLL) return p;
+    // every offset must fit 31 bits
+    for (int v = -1; v < d.n_inputs; ++v)
+    {
+        int64_t reach = 0;
+        for (int l = 0; l < d.n_loops; ++l)
+        {
+            const int64_t step = v < 0 ? d.out_step[l] : d.in_step[v][l];
+            if (step < 0) return p;
+            reach += (d.extent[l] - 1) * step;
+        }
+        if (reach >= 0x7fffffffLL) return p;
+    }
+    // Loads per term: an input carrying the blocked index is loaded per entry, the others once per
+    // thread; the leading inputs without the innermost contracted index only once per pass of it.
+    // Take the cheapest loop; on ties rather not the fastest output index (whose inputs are the
+    // ones read with unit stride across a warp), and rather an inner loop than an outer one.
+    const int inner = d.n_loops - 1;
+    int hoist = 0;
+    while (hoist < d.n_inputs && d.in_step[hoist][inner] == 0) ++hoist;
+    double best = 0.0;
+    for (int v = 0; v < d.n_inputs; ++v) best += v < hoist ? 1.0 / static_cast<double>(d.extent[inner]) : 1.0;
+    static const int kEntries[4] = {4, 5, 3, 2};
+    for (int turn = 0; turn < d.n_outer; ++turn)
+    {
+        const int l = turn < d.n_outer - 1 ? d.n_outer - 2 - turn : d.n_outer - 1;
+        for (int e = 0; e < 4; ++e)
+        {
+            const int r = kEntries[e];
+            if (d.extent[l] % r != 0 || outer_points / r < 148 * 512) continue;
+            double loads = 0.0;
+            for (int v = 0; v < d.n_inputs; ++v)
+            {
+                const double weight = v < hoist ? 1.0 / static_cast<double>(d.extent[inner]) : 1.0;
+                loads += d.in_step[v][l] != 0 ? weight : weight / r;
+            }
+            if (loads < best - 1e-9)
+            {
+                best = loads;
+                p.loop = l;
+                p.entries = r;
+            }
+        }
+    }
+    return p;
+}
+
+template <int N_IN>
+void launch_blocked(const BlockedArgs &a, int entries, double *out, const InputPointers &ins, unsigned int coarse_points,
+                    int grid, cudaStream_t s)
+{
+    switch (entries)
+    {
+        case 2: generic_blocked_kernel<N_IN, 2><<<grid, 256, 0, s>>>(a, out, ins, coarse_points); break;
+        case 3: generic_blocked_kernel<N_IN, 3><<<grid, 256, 0, s>>>(a, out, ins, coarse_points); break;
+        case 4: generic_blocked_kernel<N_IN, 4><<<grid, 256, 0, s>>>(a, out, ins, coarse_points); break;
+        default: generic_blocked_kernel<N_IN, 5><<<grid, 256, 0, s>>>(a, out, ins, coarse_points); break;
+    }
+}
+
 // Few output entries but a long contraction (for example "S_a = X_n_a Y_n_a"): the terms of
 // every output entry are cut into `chunks` contiguous ranges, one CTA per (entry, range); the
 // threads of a CTA take interleaved terms (coalesced for a unit-stride innermost index) and
@@ -307,6 +531,15 @@ extern "C" int acro_b200_generic_uses_wide_kernel(const acro_b200_generic_desc *
     return (desc != nullptr && wide_plan(*desc).chunks > 0) ? 1 : 0;
 }
 
+// Entries per thread (1 = no blocking) and the blocked outer loop that the launch would use.
+extern "C" int acro_b200_generic_blocking(const acro_b200_generic_desc *desc, int *loop)
+{
+    if (desc == nullptr || wide_plan(*desc).chunks > 0) return 1;
+    const BlockedPlan bp = blocked_plan(*desc);
+    if (loop != nullptr) *loop = bp.loop;
+    return bp.entries;
+}
+
 extern "C" size_t acro_b200_generic_scratch_bytes(const acro_b200_generic_desc *desc)
 {
     return desc != nullptr ? wide_plan(*desc).total_bytes : 0;
@@ -357,6 +590,44 @@ extern "C" int acro_b200_generic_launch(const acro_b200_generic_desc *desc, doub
             default: generic_wide_kernel<0><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, terms, ws); break;
         }
         return launch_status("acro_b200_generic_launch (wide)");
+    }
+    const BlockedPlan bp = blocked_plan(*desc);
+    if (bp.entries > 1)
+    {
+        BlockedArgs a;
+        std::memset(&a, 0, sizeof a);
+        a.n_outer = desc->n_outer;
+        a.n_loops = desc->n_loops;
+        a.op = desc->op;
+        const int inner = desc->n_loops - 1;
+        a.mid_terms = static_cast<int>(terms / desc->extent[inner]);
+        for (int l = 0; l < desc->n_loops; ++l)
+        {
+            a.extent[l] = static_cast<int>(l == bp.loop ? desc->extent[l] / bp.entries : desc->extent[l]);
+            a.out_step[l] = static_cast<int>(desc->out_step[l]);
+            for (int v = 0; v < desc->n_inputs; ++v) a.in_step[v][l] = static_cast<int>(desc->in_step[v][l]);
+        }
+        a.blk_out = static_cast<int>(a.extent[bp.loop] * desc->out_step[bp.loop]);
+        bool leading = true;
+        for (int v = 0; v < desc->n_inputs; ++v)
+        {
+            a.blk_in[v] = static_cast<int>(a.extent[bp.loop] * desc->in_step[v][bp.loop]);
+            if (desc->in_step[v][bp.loop] != 0) a.dep_mask |= 1u << v;
+            leading = leading && desc->in_step[v][inner] == 0;
+            if (leading) a.hoist = v + 1;
+        }
+        const int64_t coarse = outer_points / bp.entries;
+        const int64_t blocks = (coarse + 255) / 256;
+        const int64_t most = static_cast<int64_t>(sm_count()) * 32;
+        const int grid_b = static_cast<int>(blocks < most ? blocks : most);
+        switch (desc->n_inputs)
+        {
+            case 2: launch_blocked<2>(a, bp.entries, out, ins, static_cast<unsigned int>(coarse), grid_b, s); break;
+            case 3: launch_blocked<3>(a, bp.entries, out, ins, static_cast<unsigned int>(coarse), grid_b, s); break;
+            case 4: launch_blocked<4>(a, bp.entries, out, ins, static_cast<unsigned int>(coarse), grid_b, s); break;
+            default: launch_blocked<5>(a, bp.entries, out, ins, static_cast<unsigned int>(coarse), grid_b, s); break;
+        }
+        return launch_status("acro_b200_generic_launch (blocked)");
     }
     const int64_t blocks_needed = (outer_points + 255) / 256;
     const int64_t cap = static_cast<int64_t>(sm_count()) * 32;

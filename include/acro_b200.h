@@ -103,6 +103,14 @@ int acro_b200_generic_launch(const acro_b200_generic_desc *desc, double *out,
  * buffer must not overlap on the device. */
 int acro_b200_generic_uses_wide_kernel(const acro_b200_generic_desc *desc);
 size_t acro_b200_generic_scratch_bytes(const acro_b200_generic_desc *desc);
+/* Other shapes with 2..5 inputs whose offsets fit 31 bits run a register-blocked variant when
+ * some outer loop is not carried by every input: a thread owns 2..5 output entries along that
+ * loop, loads the inputs without it once for all of them, and multiplies the leading inputs
+ * without the innermost contracted index once per pass of that index (what the reference's
+ * generator gets from its shared-memory preloads and hoisted loops,
+ * exec/CudaExecutor.cpp:193-375).  Operation order per entry is unchanged: bit-identical
+ * results.  Returns the entries per thread (1 = not blocked) and, in *loop, the blocked loop. */
+int acro_b200_generic_blocking(const acro_b200_generic_desc *desc, int *loop);
 
 /*
  * reduce_batch:  out[f] (op)= sum_{n<rows} A[n*F + f] * (w ? w[n] : 1),  f < F.
