@@ -91,6 +91,17 @@ SIGNATURES = {
     "acro_b200_batch_inv_det": (_I, [_P, _P, _P, _I64, _I, _P]),
     "acro_b200_flat_scatter": (_I, [_P, _P, _P, _I64, _P]),
     "acro_b200_flat_sum_gather": (_I, [_P, _P, _P, _P, _I64, _P]),
+    "acro_b200_halo_mark_touched": (_I, [_P, _I64, _I64, _P]),
+    "acro_b200_halo_create": (_I, [_I, _I, _I64, _P, _I, ctypes.POINTER(_P), _P]),
+    "acro_b200_halo_counts": (_I, [_P, ctypes.POINTER(_I64), ctypes.POINTER(_I64), ctypes.POINTER(_I64)]),
+    "acro_b200_halo_copy_plan": (_I, [_P, _P, _P, _P, _P, _P]),
+    "acro_b200_halo_connect": (_I, [_P, _P]),
+    "acro_b200_halo_inbox": (_P, [_P]),
+    "acro_b200_halo_connect_pointers": (_I, [_P, _P]),
+    "acro_b200_halo_send": (_I, [_P, _P, _P]),
+    "acro_b200_halo_combine": (_I, [_P, _P, _P]),
+    "acro_b200_halo_exchange_sum": (_I, [_P, _P, _P]),
+    "acro_b200_halo_destroy": (_I, [_P]),
     "acro_index_mapping_create": (_I, [_I, _I, ctypes.POINTER(_P)]),
     "acro_index_mapping_destroy": (_I, [_P]),
     "acro_index_mapping_data": (_P, [_P]),
@@ -102,6 +113,7 @@ SIGNATURES = {
     "acro_engine_batch_matrix_inv_det": (_I, [_P, _P, _P, _P]),
     "acro_engine_flat_indexed_scatter": (_I, [_P, _P, _P, _P]),
     "acro_engine_flat_indexed_sum_gather": (_I, [_P, _P, _P, _P]),
+    "acro_engine_flat_indexed_sum_gather_shared": (_I, [_P, _P, _P, _P, _P]),
     "acro_tensor_create": (_I, [_I, ctypes.POINTER(_I), _P, _P, _I, ctypes.POINTER(_P)]),
     "acro_tensor_slice": (_I, [_P, _I, ctypes.POINTER(_I), ctypes.POINTER(_P)]),
     "acro_tensor_destroy": (_I, [_P]),

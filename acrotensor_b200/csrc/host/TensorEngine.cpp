@@ -223,6 +223,13 @@ void TensorEngine::FlatIndexedSumGather(Tensor &Aout, Tensor &Ain, IndexMapping 
               "flat_sum_gather");
 }
 
+void TensorEngine::FlatIndexedSumGather(Tensor &Aout, Tensor &Ain, IndexMapping &M, void *halo)
+{
+    ACROBATIC_ASSERT(halo != nullptr, "FlatIndexedSumGather over a sharded range needs a shared-entry exchange.");
+    FlatIndexedSumGather(Aout, Ain, M);
+    check_abi(acro_b200_halo_exchange_sum(static_cast<acro_b200_halo *>(halo), Aout.GetDeviceData(), Stream()), "halo_exchange_sum");
+}
+
 TensorKernel *TensorEngine::GetAddTensorKernel(std::string &kernel_str)
 {
     auto it = KernelMap.find(kernel_str);

@@ -352,6 +352,16 @@ int acro_engine_flat_indexed_sum_gather(acro_engine *e, acro_tensor *Aout, acro_
     });
 }
 
+int acro_engine_flat_indexed_sum_gather_shared(acro_engine *e, acro_tensor *Aout, acro_tensor *Ain, acro_index_mapping *m,
+                                               acro_b200_halo *halo)
+{
+    return guarded([&] {
+        if (e == nullptr || Aout == nullptr || Ain == nullptr || m == nullptr || halo == nullptr)
+            acro::throw_error("acro_engine_flat_indexed_sum_gather_shared: null handle");
+        e->te.FlatIndexedSumGather(*Aout->t, *Ain->t, m->m, halo);
+    });
+}
+
 int acro_b200_set_stream(void *stream)
 {
     acro::setCudaStream(stream);

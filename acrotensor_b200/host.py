@@ -234,6 +234,71 @@ class PeerGroup:
             _lib._lib.acro_b200_peer_group_destroy(h)
 
 
+class SharedEntryExchange:
+    """Sums the domain entries of a sharded IndexMapping that several ranks reach (one process per GPU
+    of one node); completes FlatIndexedSumGather when the range is cut into one slab per rank.
+    ``exchange(bytes) -> [bytes of every rank in rank order]`` is supplied by the caller (e.g.
+    torch.distributed.all_gather_object) and is called with the touched-entry bitmap, then with the CUDA
+    IPC handle of this rank's inbox.  ``on_device=False`` builds the host-side plan only (no CUDA call);
+    ``connect=False`` leaves the inboxes unconnected for :meth:`connect_pointers` (ranks of one process)."""
+
+    def __init__(self, mapping, world, rank, exchange=None, on_device=True, connect=True):
+        self.world, self.rank, self.domain_size = int(world), int(rank), mapping.GetDomainSize()
+        nbytes = (self.domain_size + 7) // 8
+        mine = ctypes.create_string_buffer(nbytes)
+        m = np.ascontiguousarray(mapping.numpy(), dtype=np.int32)
+        check(lib().acro_b200_halo_mark_touched(m.ctypes.data_as(ctypes.c_void_p), m.size, self.domain_size, mine))
+        if world > 1:
+            if exchange is None:
+                raise ValueError("an exchange over more than one rank needs an exchange function")
+            everyone = exchange(mine.raw)
+            assert len(everyone) == world and all(len(b) == nbytes for b in everyone)
+        else:
+            everyone = [mine.raw]
+        h = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(_lib.IPC_HANDLE_BYTES)
+        check(lib().acro_b200_halo_create(self.world, self.rank, self.domain_size, b"".join(everyone), int(bool(on_device)),
+                                          ctypes.byref(h), handle))
+        self._h = h
+        if on_device and connect and world > 1:
+            handles = exchange(handle.raw)
+            assert len(handles) == world and all(len(b) == _lib.IPC_HANDLE_BYTES for b in handles)
+            check(lib().acro_b200_halo_connect(self._h, b"".join(handles)))
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h is not None and _lib._lib is not None:
+            _lib._lib.acro_b200_halo_destroy(h)
+
+    def counts(self):
+        """(shared entries of this rank, (entry, other rank) pairs, doubles per half of this rank's inbox)."""
+        a, b, c = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+        check(lib().acro_b200_halo_counts(self._h, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)))
+        return a.value, b.value, c.value
+
+    def plan(self):
+        """The plan arrays as numpy int32: shared_idx, entry_off, entry_peer, entry_send, entry_recv."""
+        ns, ne, _ = self.counts()
+        arrays = [np.zeros(n, dtype=np.int32) for n in (ns, ns + 1, ne, ne, ne)]
+        check(lib().acro_b200_halo_copy_plan(self._h, *[a.ctypes.data_as(ctypes.c_void_p) for a in arrays]))
+        return arrays
+
+    def inbox(self):
+        return lib().acro_b200_halo_inbox(self._h)
+
+    def connect_pointers(self, inboxes):
+        check(lib().acro_b200_halo_connect_pointers(self._h, (ctypes.c_void_p * self.world)(*inboxes)))
+
+    def send(self, device_pointer, stream=None):
+        check(lib().acro_b200_halo_send(self._h, ctypes.c_void_p(device_pointer), stream))
+
+    def combine(self, device_pointer, stream=None):
+        check(lib().acro_b200_halo_combine(self._h, ctypes.c_void_p(device_pointer), stream))
+
+    def exchange_sum(self, device_pointer, stream=None):
+        check(lib().acro_b200_halo_exchange_sum(self._h, ctypes.c_void_p(device_pointer), stream))
+
+
 class TensorEngine:
     """acro::TensorEngine.  ``TE("S_i_j = A_n_i_j B_n", S, A, B)`` runs one contraction;
     Begin/EndMultiKernelLaunch record several and run them as one unit."""
@@ -290,8 +355,13 @@ class TensorEngine:
     def FlatIndexedScatter(self, Aout, Ain, M):
         check(lib().acro_engine_flat_indexed_scatter(self._h, Aout._h, Ain._h, M._h))
 
-    def FlatIndexedSumGather(self, Aout, Ain, M):
-        check(lib().acro_engine_flat_indexed_sum_gather(self._h, Aout._h, Ain._h, M._h))
+    def FlatIndexedSumGather(self, Aout, Ain, M, shared=None):
+        """``shared``: a SharedEntryExchange when M maps this rank's slab of a sharded range; the domain
+        entries shared with other ranks are then summed over them (collective over the ranks)."""
+        if shared is None:
+            check(lib().acro_engine_flat_indexed_sum_gather(self._h, Aout._h, Ain._h, M._h))
+        else:
+            check(lib().acro_engine_flat_indexed_sum_gather_shared(self._h, Aout._h, Ain._h, M._h, shared._h))
 
     def Clear(self):
         check(lib().acro_engine_clear(self._h))

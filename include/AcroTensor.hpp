@@ -5,4 +5,5 @@
 #include "Executor.hpp"
 #include "SliceTensor.hpp"
 #include "IndexMapping.hpp"
+#include "SharedEntryExchange.hpp"
 #endif

@@ -81,6 +81,10 @@ class TensorEngine
     // Aout[i] = Ain[M[i]]   /   Aout[M[i]] += Ain[i] (Aout zeroed first)
     void FlatIndexedScatter(Tensor &Aout, Tensor &Ain, IndexMapping &M);
     void FlatIndexedSumGather(Tensor &Aout, Tensor &Ain, IndexMapping &M);
+    // Sharded form (no counterpart in the reference): M maps this rank's slab of the range; after the
+    // local sum the domain entries shared with other ranks are summed over them through `halo`
+    // (an acro_b200_halo, see acro_b200.h, or a SharedEntryExchange).  Collective over the ranks.
+    void FlatIndexedSumGather(Tensor &Aout, Tensor &Ain, IndexMapping &M, void *halo);
 
     void Clear();
     bool IsGPUAvailable() { return isCudaReady(); }

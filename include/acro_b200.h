@@ -264,6 +264,48 @@ int acro_b200_flat_scatter(double *Aout, const double *Ain, const int *map, int6
 int acro_b200_flat_sum_gather(double *Aout, const double *Ain, const int *inv_map, const int *inv_offsets,
                               int64_t domain_size, void *stream);
 
+/*
+ * Shared-entry exchange for a sharded FlatIndexedSumGather.  No counterpart in the reference,
+ * which is single-GPU.  The range of an IndexMapping (element-local entries) is cut into one
+ * slab per rank (one process per GPU of one node); after acro_b200_flat_sum_gather over its own
+ * slab a rank holds partial sums, and the domain entries reached from several ranks' slabs must
+ * be summed over those ranks.
+ *   mark_touched  host helper: bitmap ((domain_size + 7) / 8 bytes, bit d = some map value equals d)
+ *   create        takes the world bitmaps in rank order (exchanged by the host program), derives which
+ *                 entries this rank shares with which ranks and every rank's inbox layout; with
+ *                 on_device = 1 it also allocates this rank's inbox on the current device and returns
+ *                 its CUDA IPC handle.  on_device = 0 makes a host-side plan only (no CUDA call) whose
+ *                 arrays copy_plan returns: for shared entry k (domain position shared_idx[k], ascending),
+ *                 pairs entry_off[k] .. entry_off[k+1]-1 name the other ranks reaching it (entry_peer,
+ *                 ascending), the slot this rank writes in that rank's inbox (entry_send) and the slot of
+ *                 its own inbox where that rank's value arrives (entry_recv).
+ *   connect       maps the other ranks' inboxes from their IPC handles (world * ACRO_B200_IPC_HANDLE_BYTES
+ *                 bytes, rank order); connect_pointers does the same from device pointers for ranks that
+ *                 live in one process (acro_b200_halo_inbox gives a rank's own pointer).
+ *   send          stores this rank's value of every shared entry into the inboxes of the ranks sharing it
+ *                 (remote stores over NVLink peer mappings) and publishes the call's sequence number;
+ *   combine       waits (bounded; a wait that gives up shows in acro_b200_device_status) for the ranks it
+ *                 shares entries with and replaces every shared entry of `values` by the sum over all
+ *                 sharing ranks in ascending rank order, so every rank holds identical bits.
+ *   exchange_sum  = send, then combine, on the same stream.
+ * All ranks must issue the same sequence of send/combine calls; ranks of ONE process sharing a GPU must
+ * launch every send before the first combine on one stream, so that no kernel waits for a later one.
+ */
+typedef struct acro_b200_halo acro_b200_halo;
+int acro_b200_halo_mark_touched(const int *map, int64_t range_size, int64_t domain_size, unsigned char *bitmap);
+int acro_b200_halo_create(int world, int rank, int64_t domain_size, const unsigned char *all_bitmaps, int on_device,
+                          acro_b200_halo **out, unsigned char *handle_out);
+int acro_b200_halo_counts(const acro_b200_halo *halo, int64_t *shared_entries, int64_t *sharing_pairs, int64_t *inbox_doubles);
+int acro_b200_halo_copy_plan(const acro_b200_halo *halo, int *shared_idx, int *entry_off, int *entry_peer, int *entry_send,
+                             int *entry_recv);
+int acro_b200_halo_connect(acro_b200_halo *halo, const unsigned char *all_handles);
+void *acro_b200_halo_inbox(const acro_b200_halo *halo);
+int acro_b200_halo_connect_pointers(acro_b200_halo *halo, void *const *inboxes);
+int acro_b200_halo_send(acro_b200_halo *halo, const double *values, void *stream);
+int acro_b200_halo_combine(acro_b200_halo *halo, double *values, void *stream);
+int acro_b200_halo_exchange_sum(acro_b200_halo *halo, double *values, void *stream);
+int acro_b200_halo_destroy(acro_b200_halo *halo);
+
 /* ---------------------------------------------------------------- engine layer */
 
 typedef struct acro_tensor acro_tensor;   /* an acro::Tensor */
@@ -335,6 +377,10 @@ int acro_engine_batch_matrix_inv_det(acro_engine *e, acro_tensor *Ainv, acro_ten
 /* FlatIndexedScatter / FlatIndexedSumGather, kernel/TensorEngine.cpp:693-716. */
 int acro_engine_flat_indexed_scatter(acro_engine *e, acro_tensor *Aout, acro_tensor *Ain, acro_index_mapping *m);
 int acro_engine_flat_indexed_sum_gather(acro_engine *e, acro_tensor *Aout, acro_tensor *Ain, acro_index_mapping *m);
+/* The same over this rank's slab of the range, followed by the sum of the shared domain entries over the
+ * ranks (acro_b200_halo_exchange_sum); `halo` was created from the touched-entry bitmaps of all ranks. */
+int acro_engine_flat_indexed_sum_gather_shared(acro_engine *e, acro_tensor *Aout, acro_tensor *Ain, acro_index_mapping *m,
+                                               acro_b200_halo *halo);
 
 /* Stream used by the calling host thread's tensor copies / fills and by engines without their
  * own stream (per thread; NULL = legacy default stream). */

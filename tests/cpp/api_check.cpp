@@ -176,6 +176,20 @@ static void device_checks()
     TE.EndMultiKernelLaunch();
     Aout.MoveFromGPU();
     CHECK(Aout(0) == 3.0 && Aout(1) == 3.0 && Aout(2) == 3.0);
+
+    // sum-gather over a sharded range: one rank shares nothing, the result is the plain one
+    IndexMapping Map(4, 6);
+    const int targets[6] = {0, 1, 1, 3, 0, 1};
+    for (int i = 0; i < 6; ++i) Map[i] = targets[i];
+    SharedEntryExchange Exchange(Map, 1, 0, [](const SharedEntryExchange::Bytes &mine) {
+        return std::vector<SharedEntryExchange::Bytes>(1, mine);
+    });
+    CHECK(Exchange.GetNumShared() == 0);
+    Tensor In(6), Out(4);
+    for (int i = 0; i < 6; ++i) In(i) = i + 1;
+    TE.FlatIndexedSumGather(Out, In, Map, Exchange);
+    Out.MoveFromGPU();
+    CHECK(Out(0) == 6.0 && Out(1) == 11.0 && Out(2) == 0.0 && Out(3) == 4.0);
 }
 
 int main(int argc, char **argv)
