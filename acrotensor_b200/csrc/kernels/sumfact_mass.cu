@@ -14,8 +14,8 @@
 // contracts k3, which crosses the plane owners: Y2 goes through shared memory and thread
 // (e, i1) finishes V_e_i1_*_* and writes it over its own Y2 slots (read into registers
 // first), so V needs no buffer of its own and three CTAs fit on an SM.  Tiles of 32 elements; U and W tiles arrive by asynchronous
-// bulk copies (per element for U, into slots padded to 66 doubles so that the elements of a
-// warp fall into different banks; one span for W), issued as soon as the previous tile's
+// bulk copies (per element for U, into slots padded by two doubles so that the elements of a
+// warp fall into different banks, or one span when the element size is odd; one span for W), issued as soon as the previous tile's
 // copies are dead, so they overlap the rest of that tile and the other CTA of the SM.
 #include "common.cuh"
 #include "tma.cuh"
@@ -34,8 +34,11 @@ struct Geo
     static constexpr int P = P_, Q = Q_, CTAS = CTAS_;
     static constexpr int NT = ET * Q;                                 // threads per CTA
     static constexpr int U_ELEM = P * P * P, W_ELEM = Q * Q * Q;
-    static constexpr int U_STRIDE = U_ELEM + 2 - (U_ELEM % 2);        // padded, even (16-byte multiple)
-    static constexpr bool U_BULK = (U_ELEM % 2 == 0);                 // an element of U is a 16-byte multiple
+    // Even element size: slots padded by two doubles, so that the elements of a warp fall into different
+    // banks and every slot stays a 16-byte multiple (one bulk copy per element).  Odd element size: the
+    // unpadded odd stride is already conflict-free, and the tile travels as one contiguous span.
+    static constexpr bool U_ODD = (U_ELEM % 2 != 0);
+    static constexpr int U_STRIDE = U_ODD ? U_ELEM : U_ELEM + 2;
     static constexpr int Y_ROW = P * Q;                               // Y2 row of one (element, i1); V reuses the first P*P
     static constexpr int Y_MIN = P * P * Q;
     static constexpr int Y_STRIDE = Y_MIN + ((Q - Y_MIN % 16) % 16 + 16) % 16;   // = Q mod 16: plane owners of a half warp hit distinct banks
@@ -70,9 +73,10 @@ __device__ __forceinline__ void issue_tile_load(Smem<G> &s, const MassArgs &a, i
     if (threadIdx.x < 32)
     {
         const int64_t e0 = tile * ET;
-        if (threadIdx.x == 0) mbar_arrive_expect_tx(&s.bar, ET * ((G::U_BULK ? G::U_ELEM : 0) + G::W_ELEM) * 8);
+        if (threadIdx.x == 0) mbar_arrive_expect_tx(&s.bar, ET * (G::U_ELEM + G::W_ELEM) * 8);
         __syncwarp();
-        if (G::U_BULK) bulk_load(s.U + threadIdx.x * G::U_STRIDE, a.U + (e0 + threadIdx.x) * G::U_ELEM, G::U_ELEM * 8, &s.bar);
+        if (!G::U_ODD) bulk_load(s.U + threadIdx.x * G::U_STRIDE, a.U + (e0 + threadIdx.x) * G::U_ELEM, G::U_ELEM * 8, &s.bar);
+        else if (threadIdx.x == 0) bulk_load(s.U, a.U + e0 * G::U_ELEM, ET * G::U_ELEM * 8, &s.bar);
         if (threadIdx.x == 0) bulk_load(s.W, a.W + e0 * G::W_ELEM, ET * G::W_ELEM * 8, &s.bar);
     }
 }
@@ -121,17 +125,14 @@ sumfact_mass_kernel(const MassArgs a)
         const int n_e = left < ET ? static_cast<int>(left) : ET;
         const bool by_bulk = a.use_bulk && tile < n_tiles_full;
 
-        if (!by_bulk || !G::U_BULK)
-        {
-            // U by plain coalesced loads into the padded slots (ragged / unaligned tile, or odd element size)
-            for (int i = tid; i < n_e * U_ELEM; i += NT) s.U[(i / U_ELEM) * U_STRIDE + (i % U_ELEM)] = __ldcs(a.U + e0 * U_ELEM + i);
-        }
         if (!by_bulk)
         {
+            // plain coalesced loads (ragged or unaligned tile)
+            for (int i = tid; i < n_e * U_ELEM; i += NT) s.U[(i / U_ELEM) * U_STRIDE + (i % U_ELEM)] = __ldcs(a.U + e0 * U_ELEM + i);
             for (int i = tid; i < n_e * W_ELEM; i += NT) s.W[i] = __ldcs(a.W + e0 * W_ELEM + i);
+            __syncthreads();
         }
-        if (!by_bulk || !G::U_BULK) __syncthreads();
-        if (by_bulk)
+        else
         {
             if (!mbar_wait(&s.bar, parity)) atomicExch(a.wait_flag, 1);
             parity ^= 1u;
@@ -259,6 +260,10 @@ sumfact_mass_kernel(const MassArgs a)
 typedef Geo<4, 5, 3> Geo45;   // p = 3 hexahedra: 4 dofs, 5 quadrature points per direction
 typedef Geo<3, 4, 4> Geo34;   // p = 2
 typedef Geo<2, 3, 6> Geo23;   // p = 1
+typedef Geo<2, 4, 6> Geo24;   // the same orders with one more quadrature point per direction
+typedef Geo<3, 5, 4> Geo35;
+typedef Geo<4, 6, 2> Geo46;
+typedef Geo<5, 6, 1> Geo56;   // p = 4
 
 template <class G>
 int launch_mass(const MassArgs &args, int sms, cudaStream_t stream)
@@ -278,13 +283,13 @@ int launch_mass(const MassArgs &args, int sms, cudaStream_t stream)
 
 extern "C" {
 
-int acro_b200_sumfact_mass_supported(int p, int q) { return ((p == 4 && q == 5) || (p == 3 && q == 4) || (p == 2 && q == 3)) ? 1 : 0; }
+int acro_b200_sumfact_mass_supported(int p, int q) { return (p >= 2 && p <= 5 && (q == p + 1 || (q == p + 2 && p <= 4))) ? 1 : 0; }
 
 int acro_b200_sumfact_mass(const double *B, const double *U, const double *W, double *V, int64_t elements, int p, int q, void *stream)
 {
     if (B == nullptr || U == nullptr || W == nullptr || V == nullptr) return fail_invalid("acro_b200_sumfact_mass: null argument");
     if (elements < 1) return fail_invalid("acro_b200_sumfact_mass: element count must be positive");
-    if (!acro_b200_sumfact_mass_supported(p, q)) return fail_unsupported("acro_b200_sumfact_mass: instantiated for (p, q) = (2, 3), (3, 4), (4, 5)");
+    if (!acro_b200_sumfact_mass_supported(p, q)) return fail_unsupported("acro_b200_sumfact_mass: instantiated for (p, q) = (2, 3), (2, 4), (3, 4), (3, 5), (4, 5), (4, 6), (5, 6)");
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_sumfact_mass");
 
@@ -298,9 +303,10 @@ int acro_b200_sumfact_mass(const double *B, const double *U, const double *W, do
     if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_sumfact_mass (status flag)");
     args.use_bulk = (aligned16(U) && aligned16(W)) ? 1 : 0;
     cudaStream_t s = as_stream(stream);
-    if (p == 4) return launch_mass<Geo45>(args, sms, s);
-    if (p == 3) return launch_mass<Geo34>(args, sms, s);
-    return launch_mass<Geo23>(args, sms, s);
+    if (p == 5) return launch_mass<Geo56>(args, sms, s);
+    if (p == 4) return q == 5 ? launch_mass<Geo45>(args, sms, s) : launch_mass<Geo46>(args, sms, s);
+    if (p == 3) return q == 4 ? launch_mass<Geo34>(args, sms, s) : launch_mass<Geo35>(args, sms, s);
+    return q == 3 ? launch_mass<Geo23>(args, sms, s) : launch_mass<Geo24>(args, sms, s);
 }
 
 }

@@ -237,7 +237,7 @@ int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t 
  *   V_e_i1_i2_i3 = sum B_k3_i3 B_k2_i2 B_k1_i1 W_e_k1_k2_k3 (sum B_k1_j1 B_k2_j2 B_k3_j3 U_e_j1_j2_j3),
  * evaluated stage by stage (contract i3, i2, i1, scale by W, contract k1, k2, k3) with every
  * intermediate kept in registers / shared memory.  B is [q][p], U and V are [elements][p][p][p],
- * W is [elements][q][q][q]; instantiated for (p, q) = (2,3), (3,4), (4,5).  HBM traffic:
+ * W is [elements][q][q][q]; instantiated for (p, q) = (2,3), (2,4), (3,4), (3,5), (4,5), (4,6), (5,6).  HBM traffic:
  * 8*(2p^3 + q^3) bytes per element.  Replaces the
  * reference's fused multi-kernel launch (exec/CudaExecutor.cpp:69-102,286-323), which still
  * writes every intermediate tensor to global memory (:536).

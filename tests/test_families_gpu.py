@@ -101,11 +101,12 @@ def run_chain_oracle(b, u, w):
     return t["V"]
 
 
-@pytest.mark.parametrize("elements,offset,p", [(1, 0, 4), (31, 0, 4), (32, 0, 4), (33, 0, 4), (1000, 0, 4), (65, 1, 4), (10007, 0, 4),
-                                                (1, 0, 3), (100, 0, 3), (5001, 1, 3), (33, 0, 2), (20000, 0, 2), (77, 1, 2)])
-def test_sumfact_mass_kernel(torch, elements, offset, p):
+@pytest.mark.parametrize("elements,offset,p,q", [(1, 0, 4, 5), (31, 0, 4, 5), (32, 0, 4, 5), (33, 0, 4, 5), (1000, 0, 4, 5), (65, 1, 4, 5),
+                                                  (10007, 0, 4, 5), (1, 0, 3, 4), (100, 0, 3, 4), (5001, 1, 3, 4), (33, 0, 2, 3),
+                                                  (20000, 0, 2, 3), (77, 1, 2, 3), (3001, 0, 2, 4), (95, 1, 2, 4), (2049, 0, 3, 5),
+                                                  (64, 1, 3, 5), (1500, 0, 4, 6), (33, 1, 4, 6), (999, 0, 5, 6), (32, 1, 5, 6)])
+def test_sumfact_mass_kernel(torch, elements, offset, p, q):
     rng = np.random.default_rng(elements)
-    q = p + 1
     b = rng.random((q, p)) * 2 - 1
     u = rng.random((elements, p, p, p)) * 2 - 1
     w = rng.random((elements, q, q, q)) + 0.5
@@ -115,7 +116,7 @@ def test_sumfact_mass_kernel(torch, elements, offset, p):
     ku, pu = to_dev(torch, u, offset)
     kw, pw = to_dev(torch, w)
     kv, pv = to_dev(torch, np.full(ref.shape, -1.0))
-    assert lib().acro_b200_sumfact_mass_supported(p, q) == 1 and lib().acro_b200_sumfact_mass_supported(5, 6) == 0
+    assert lib().acro_b200_sumfact_mass_supported(p, q) == 1 and lib().acro_b200_sumfact_mass_supported(6, 7) == 0
     check(lib().acro_b200_sumfact_mass(pb, pu, pw, pv, elements, p, q, None))
     status_ok()
     got = kv.cpu().numpy().reshape(ref.shape)
