@@ -473,43 +473,119 @@ def spot_check(workloads, sessions, batches, world):
 
 
 def run_ops(args):
-    """Side measurement (not part of the suite): the batched 3x3 inverse + determinant that
-    produces cfg 3's inputs, on [2^20, 64, 3, 3], device resident, through the engine API."""
+    """Side measurements (not part of the suite), device resident, through the engine API: the batched
+    3x3 inverse + determinant that produces cfg 3's inputs on [2^20, 64, 3, 3] (the headline of this
+    line), the flat-indexed scatter / sum-gather either side of an operator chain, the mass-operator
+    chain at its other compiled geometries, and two finite-element assembly strings of the reference's
+    own tests that run on the generic kernel."""
     import torch
     import acrotensor_b200 as ab
     torch.cuda.set_device(0)
+    hbm_peak, kind = measured_peaks()
+    te = ab.TensorEngine("Cuda")
+
+    def dev_tensor(shape, lo=0.0, hi=1.0, seed=7):
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(seed)
+        return torch.rand(shape, generator=gen, device="cuda", dtype=torch.float64) * (hi - lo) + lo
+
+    def bind(t):
+        return ab.Tensor(tuple(t.shape), hdata=torch.empty(tuple(t.shape), dtype=torch.float64).numpy(), ddata=t, ongpu=True)
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / args.steps
+
+    def entry(ms, nbytes, note):
+        return {"ms": round(ms, 4), "GBps": round(nbytes / ms * 1e-6, 1), "frac_hbm": round(nbytes / ms * 1e-6 / hbm_peak, 4), "what": note}
+
+    per_op = {}
     E = max(1, int((1 << 20) * args.scale))
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(7)
-    J = torch.rand((E, 64, 3, 3), generator=gen, device="cuda", dtype=torch.float64) * 0.4 - 0.2
+
+    # batched inverse + determinant
+    J = dev_tensor((E, 64, 3, 3), -0.2, 0.2)
     for d in range(3):
         J[..., d, d] += 1.0
     inv, det = torch.empty_like(J), torch.empty((E, 64), device="cuda", dtype=torch.float64)
-    host = {n: torch.empty(t.shape, dtype=torch.float64).numpy() for n, t in (("J", J), ("inv", inv), ("det", det))}
-    TJ = ab.Tensor(J.shape, hdata=host["J"], ddata=J, ongpu=True)
-    TI = ab.Tensor(inv.shape, hdata=host["inv"], ddata=inv, ongpu=True)
-    TD = ab.Tensor(det.shape, hdata=host["det"], ddata=det, ongpu=True)
-    te = ab.TensorEngine("Cuda")
-    for _ in range(args.warmup):
-        te.BatchMatrixInvDet(TI, TD, TJ)
-    torch.cuda.synchronize()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        te.BatchMatrixInvDet(TI, TD, TJ)
-    t1.record()
-    torch.cuda.synchronize()
-    ms = t0.elapsed_time(t1) / args.steps
+    TJ, TI, TD = bind(J), bind(inv), bind(det)
+    ms = timed(lambda: te.BatchMatrixInvDet(TI, TD, TJ))
     nbytes = E * 64 * (72 + 72 + 8)
-    hbm_peak, kind = measured_peaks()
     ident = torch.einsum("ekij,eklj->ekil", J[:64], inv[:64])      # reference layout: inv holds the transposed inverse
     err = float((ident - torch.eye(3, device="cuda", dtype=torch.float64)).abs().max())
+    headline = (ms, nbytes)
+    del J, inv, det, TJ, TI, TD
+
+    # scatter / sum-gather on a 3D trilinear-like numbering: 8 entries per element, neighbours share entries
+    n = max(2, int(round(E ** (1.0 / 3.0))))
+    ex, ey, ez = torch.meshgrid(torch.arange(n), torch.arange(n), torch.arange(n), indexing="ij")
+    corner = (ex * (n + 1) + ey) * (n + 1) + ez
+    offs = torch.tensor([(a * (n + 1) + b) * (n + 1) + c for a in (0, 1) for b in (0, 1) for c in (0, 1)])
+    mapping = (corner.reshape(-1, 1) + offs.reshape(1, -1)).to(torch.int32).reshape(-1).numpy()
+    domain, rng_size = (n + 1) ** 3, mapping.size
+    M = ab.IndexMapping(domain, rng_size, mapping)
+    M.ComputeInverse()
+    x, u = dev_tensor((domain,)), torch.empty((rng_size,), device="cuda", dtype=torch.float64)
+    TX, TU = bind(x), bind(u)
+    per_op["flat_indexed_scatter"] = entry(timed(lambda: te.FlatIndexedScatter(TU, TX, M)), rng_size * 12 + domain * 8,
+                                           "%d elements x 8 entries from %d domain entries; bytes = map + output + domain once" % (n ** 3, domain))
+    per_op["flat_indexed_sum_gather"] = entry(timed(lambda: te.FlatIndexedSumGather(TX, TU, M)), rng_size * 12 + domain * 12,
+                                              "same mapping; bytes = input + inverse map + offsets + output")
+    del x, u, TX, TU, M
+
+    # the mass-operator chain at its other geometries (cfg 2 is (4,5))
+    chain = [("T1_e_i1_i2_k3 = B_k3_i3 U_e_i1_i2_i3", "T1", ["B", "U"]), ("T2_e_i1_k2_k3 = B_k2_i2 T1_e_i1_i2_k3", "T2", ["B", "T1"]),
+             ("X_e_k1_k2_k3 = B_k1_i1 T2_e_i1_k2_k3 W_e_k1_k2_k3", "X", ["B", "T2", "W"]), ("Y1_e_i1_k2_k3 = B_k1_i1 X_e_k1_k2_k3", "Y1", ["B", "X"]),
+             ("Y2_e_i1_i2_k3 = B_k2_i2 Y1_e_i1_k2_k3", "Y2", ["B", "Y1"]), ("V_e_i1_i2_i3 = B_k3_i3 Y2_e_i1_i2_k3", "V", ["B", "Y2"])]
+    for p, q in ((2, 3), (2, 4), (3, 4), (3, 5), (4, 6), (5, 6)):
+        Ec = max(1, int((1 << (19 if q >= 6 else 20)) * args.scale))
+        shapes = {"B": (q, p), "U": (Ec, p, p, p), "W": (Ec, q, q, q), "T1": (Ec, p, p, q), "T2": (Ec, p, q, q), "X": (Ec, q, q, q),
+                  "Y1": (Ec, p, q, q), "Y2": (Ec, p, p, q), "V": (Ec, p, p, p)}
+        # the transient intermediates are elided by the fused kernel; to bind they only need storage
+        # of the right size, so all five share one device buffer
+        spare = torch.empty((Ec * q * q * q,), device="cuda", dtype=torch.float64)
+        t = {}
+        for k, shape in shapes.items():
+            if k in ("B", "U", "W", "V"):
+                t[k] = bind(dev_tensor(shape, 0.5, 1.5))
+            else:
+                t[k] = ab.Tensor(shape, hdata=torch.empty(shape, dtype=torch.float64).numpy(),
+                                 ddata=spare[: int(np.prod(shape))].view(shape), ongpu=True)
+                t[k].SetTransient(True)
+
+        def step():
+            te.BeginMultiKernelLaunch()
+            for kernel, out, ins in chain:
+                te(kernel, t[out], *[t[i] for i in ins])
+            te.EndMultiKernelLaunch()
+
+        per_op["sumfact_mass_p%d_q%d" % (p, q)] = entry(timed(step), Ec * 8 * (2 * p ** 3 + q ** 3), "%d elements, six stages fused" % Ec)
+        del t, spare
+
+    # finite-element assembly strings of the reference's tests on the generic kernel (register-blocked variant)
+    Eg = max(1, int(65536 * args.scale))
+    B, D = dev_tensor((4, 4), -1, 1), dev_tensor((Eg, 4, 4))
+    Mm = torch.empty((Eg, 4, 4, 4, 4), device="cuda", dtype=torch.float64)
+    TB, TDd, TM = bind(B), bind(D), bind(Mm)
+    kernel = "M_e_i1_i2_j1_j2=B_k1_i1 B_k1_j1 B_k2_i2 B_k2_j2 D_e_k1_k2"
+    per_op["generic_mass2d_assembly"] = entry(timed(lambda: te(kernel, TM, TB, TB, TB, TB, TDd)), Eg * 8 * (256 + 16),
+                                              "%d elements, 16 terms per entry; %s" % (Eg, te.GetImplementation(kernel, TM, TB, TB, TB, TB, TDd).split("|")[-1].strip()))
+    del B, D, Mm, TB, TDd, TM
+
+    ms, nbytes = headline
     print(json.dumps({"metric": "batch_inv_det_throughput", "value": round(nbytes / ms * 1e-6, 1), "unit": "GB/s", "n_gpus": 1,
                       "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "dtype": "f64",
                       "config": {"workload": "BatchMatrixInvDet on [%d,64,3,3]" % E},
                       "roofline": {"bound": "hbm", "achieved": round(nbytes / ms * 1e-6, 1), "peak": hbm_peak, "unit": "GB/s",
                                    "frac": round(nbytes / ms * 1e-6 / hbm_peak, 4), "traffic": None},
-                      "identity_error": err}))
+                      "identity_error": err, "per_op": per_op}))
 
 
 # ----------------------------------------------------------------------------- CPU arms
