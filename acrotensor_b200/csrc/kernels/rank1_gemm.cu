@@ -29,7 +29,7 @@ using namespace acro_b200_detail;
 namespace
 {
 
-constexpr int QN = 64;                 // largest contracted extent (any multiple of 4 up to this)
+constexpr int QN = 64;                 // largest contracted extent
 constexpr int ET = 32;                 // elements per CTA tile (4 row tiles of 8)
 constexpr int LDW = QN + 4;            // padded W row
 constexpr int NTHREADS = 256;
@@ -53,7 +53,7 @@ struct Rank1Args
     const double *B2;
     double *M;
     int64_t elements;
-    int q;          // contracted extent, a multiple of 4, <= QN
+    int q;          // contracted extent, 1 .. QN
     int ni, nj;
     int op;
     int *wait_flag;
@@ -97,8 +97,13 @@ rank1_gemm_kernel(const Rank1Args a)
         mbar_init(&s.full[1], 1);
         fence_mbar_init();
     }
-    for (int i = tid; i < a.q * ni; i += NTHREADS) s.B1[i] = a.B1[i];
-    for (int i = tid; i < a.q * nj; i += NTHREADS) s.B2[i] = a.B2[i];
+    // The contracted extent is processed in steps of four: rows q .. q4-1 of B1, B2 and the same
+    // columns of every W row are zero, so that they add nothing.
+    const int q4 = (a.q + 3) & ~3;
+    for (int i = tid; i < q4 * ni; i += NTHREADS) s.B1[i] = i < a.q * ni ? a.B1[i] : 0.0;
+    for (int i = tid; i < q4 * nj; i += NTHREADS) s.B2[i] = i < a.q * nj ? a.B2[i] : 0.0;
+    for (int i = tid; i < 2 * ET * (q4 - a.q); i += NTHREADS)
+        s.W[0][(i / (q4 - a.q)) * LDW + a.q + i % (q4 - a.q)] = 0.0;     // the two buffers are contiguous: rows 0 .. 2*ET-1
     __syncthreads();
 
     int64_t tile = blockIdx.x;
@@ -145,7 +150,7 @@ rank1_gemm_kernel(const Rank1Args a)
                 for (int nt = 0; nt < NTG; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
 
 #pragma unroll 2
-            for (int k0 = 0; k0 < a.q; k0 += 4)
+            for (int k0 = 0; k0 < q4; k0 += 4)
             {
                 double af[4], bf[NTG];
 #pragma unroll
@@ -242,7 +247,7 @@ template <class C, int QC>
 __global__ void __launch_bounds__(C::THREADS, C::CTAS)
 rank1_gemm_sym_kernel(const Rank1Args a)
 {
-    const int q_ext = QC > 0 ? QC : a.q;
+    const int q_ext = QC > 0 ? QC : (a.q + 3) & ~3;     // steps of four; the padding rows / columns are zero
     constexpr int NTW = C::NTW, MT = C::MT, TE = C::TILE_E, THREADS = C::THREADS;
     extern __shared__ __align__(128) unsigned char raw[];
     const int ni = a.ni, nc = ni * ni, n_cols = ni * (ni + 1) / 2;
@@ -263,7 +268,9 @@ rank1_gemm_sym_kernel(const Rank1Args a)
         mbar_init(&full[1], 1);
         fence_mbar_init();
     }
-    for (int i = tid; i < a.q * ni; i += THREADS) sB[(i / ni) * ldb + (i % ni)] = a.B1[i];
+    for (int i = tid; i < q_ext * ni; i += THREADS) sB[(i / ni) * ldb + (i % ni)] = i < a.q * ni ? a.B1[i] : 0.0;
+    for (int i = tid; i < 2 * TE * (q_ext - a.q); i += THREADS)
+        sW[(i / (q_ext - a.q)) * LDW + a.q + i % (q_ext - a.q)] = 0.0;
     __syncthreads();
 
     // packed column c -> (i, j), row-major upper triangle; fixed per thread for the whole kernel
@@ -403,7 +410,7 @@ extern "C" {
 
 int acro_b200_rank1_gemm_supported(int q, int ni, int nj)
 {
-    return (q >= 4 && q <= QN && q % 4 == 0 && ni >= 1 && ni <= MAXN && nj >= 1 && nj <= MAXN) ? 1 : 0;
+    return (q >= 1 && q <= QN && ni >= 1 && ni <= MAXN && nj >= 1 && nj <= MAXN) ? 1 : 0;
 }
 
 int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, double *M, int64_t elements, int q, int ni, int nj,
@@ -411,7 +418,7 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
 {
     if (W == nullptr || B1 == nullptr || B2 == nullptr || M == nullptr) return fail_invalid("acro_b200_rank1_gemm: null argument");
     if (elements < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_rank1_gemm: bad element count or operator");
-    if (!acro_b200_rank1_gemm_supported(q, ni, nj)) return fail_unsupported("acro_b200_rank1_gemm: needs q a multiple of 4 up to 64 and 1 <= ni, nj <= 32");
+    if (!acro_b200_rank1_gemm_supported(q, ni, nj)) return fail_unsupported("acro_b200_rank1_gemm: needs 1 <= q <= 64 and 1 <= ni, nj <= 32");
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_rank1_gemm");
 
@@ -427,7 +434,7 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
     args.op = op;
     args.wait_flag = wait_flag_device_ptr();
     if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_rank1_gemm (status flag)");
-    args.use_bulk = aligned16(W) ? 1 : 0;
+    args.use_bulk = (aligned16(W) && q % 2 == 0) ? 1 : 0;     // a W row must be a 16-byte multiple to travel as a bulk copy
 
     const size_t smem = sizeof(Smem);
     const int64_t n_tiles = (elements + ET - 1) / ET;

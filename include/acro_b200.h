@@ -213,7 +213,7 @@ int acro_b200_pointwise_sym(const acro_b200_pointwise_desc *desc, const double *
  * rank1_gemm:  M[e,i,j] (op)= sum_{q<Q} W[e,q] * B1[q,i] * B2[q,j]   (batched element mass matrices,
  * "M_e_i_j = W_e_q B_q_i B_q_j").  One GEMM  [elements x Q] * [Q x ni*nj]  whose right operand
  * B1[q,i]*B2[q,j] is formed on the fly; fp64 tensor cores (mma.sync m8n8k4).  Instantiated
- * for Q a multiple of 4 up to 64 and ni, nj <= 32.  HBM traffic 8*(Q + ni*nj) bytes per element, 2*Q*ni*nj flops.
+ * for Q up to 64 (processed in steps of four, zero-padded on chip) and ni, nj <= 32.  HBM traffic 8*(Q + ni*nj) bytes per element, 2*Q*ni*nj flops.
  * Replaces the generated kernel (one block per element, serial 64-term sums per thread,
  * exec/CudaExecutor.cpp:193-204,520-523).
  */

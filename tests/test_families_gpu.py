@@ -41,6 +41,8 @@ def status_ok():
     (32, 27, 27, 0, 0, 64), (33, 27, 27, 0, 0, 64), (1, 27, 27, 0, 0, 64), (100, 27, 27, 1, 0, 64), (257, 27, 27, 2, 0, 64),
     (64, 5, 7, 0, 0, 64), (95, 32, 32, 0, 0, 64), (70, 27, 27, 0, 1, 64), (10000, 27, 27, 0, 0, 64), (40, 27, 27, 0, 2, 64),
     (75, 1, 1, 0, 0, 64), (50, 2, 2, 1, 0, 64), (64, 27, 27, 0, 0, 8), (100, 5, 7, 0, 0, 36), (33, 10, 10, 2, 0, 4),
+    # contracted extents that are not multiples of four (zero-padded on chip); odd ones cannot travel as bulk copies
+    (3000, 27, 27, 0, 0, 27), (77, 27, 27, 0, 2, 27), (100, 8, 8, 0, 0, 10), (41, 8, 9, 1, 1, 63), (65, 3, 3, 0, 0, 1), (90, 32, 32, 2, 0, 5),
 ])
 def test_rank1_gemm_kernel(torch, elements, ni, nj, op, offset, q):
     rng = np.random.default_rng(elements + ni)
@@ -58,7 +60,7 @@ def test_rank1_gemm_kernel(torch, elements, ni, nj, op, offset, q):
     keep_1, p1 = to_dev(torch, b1)
     keep_2, p2 = (keep_1, p1) if b2 is b1 else to_dev(torch, b2)
     keep_m, pm = to_dev(torch, m0)
-    assert lib().acro_b200_rank1_gemm_supported(q, ni, nj) == 1 and lib().acro_b200_rank1_gemm_supported(q + 1, ni, nj) == 0
+    assert lib().acro_b200_rank1_gemm_supported(q, ni, nj) == 1 and lib().acro_b200_rank1_gemm_supported(65, ni, nj) == 0
     check(lib().acro_b200_rank1_gemm(pw, p1, p2, pm, elements, q, ni, nj, op, None))
     status_ok()
     got = keep_m.cpu().numpy().reshape(m0.shape)
