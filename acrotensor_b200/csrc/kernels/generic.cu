@@ -181,6 +181,68 @@ struct BlockedArgs
     int in_step[kBlockedMaxInputs][ACRO_B200_MAX_LOOPS];
 };
 
+// One pass of the innermost contracted index for the R entries of a thread.  H leading inputs do
+// not carry that index: their product is formed once, before the loop.
+template <int N_IN, int R, int H>
+__device__ __forceinline__ void inner_pass(const BlockedArgs &a, const InputPointers &ins, const int (&off)[N_IN], int e_in, int inner,
+                                           double (&acc)[R])
+{
+    double pre[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) pre[r] = 0.0;
+#pragma unroll
+    for (int v = 0; v < H; ++v)
+    {
+        if ((a.dep_mask >> v) & 1u)
+        {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+            {
+                const double x = ins.p[v][off[v] + r * a.blk_in[v]];
+                pre[r] = (v == 0) ? x : __dmul_rn(pre[r], x);
+            }
+        }
+        else
+        {
+            const double x = ins.p[v][off[v]];
+#pragma unroll
+            for (int r = 0; r < R; ++r) pre[r] = (v == 0) ? x : __dmul_rn(pre[r], x);
+        }
+    }
+
+    int o[N_IN];
+#pragma unroll
+    for (int v = 0; v < N_IN; ++v) o[v] = off[v];
+    for (int i = 0; i < e_in; ++i)
+    {
+        double prod[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) prod[r] = pre[r];
+#pragma unroll
+        for (int v = H; v < N_IN; ++v)
+        {
+            if ((a.dep_mask >> v) & 1u)
+            {
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                {
+                    const double x = ins.p[v][o[v] + r * a.blk_in[v]];
+                    prod[r] = (v == 0) ? x : __dmul_rn(prod[r], x);
+                }
+            }
+            else
+            {
+                const double x = ins.p[v][o[v]];
+#pragma unroll
+                for (int r = 0; r < R; ++r) prod[r] = (v == 0) ? x : __dmul_rn(prod[r], x);
+            }
+            o[v] += a.in_step[v][inner];
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = __dadd_rn(acc[r], prod[r]);
+    }
+}
+
 template <int N_IN, int R>
 __global__ void __launch_bounds__(256)
 generic_blocked_kernel(const __grid_constant__ BlockedArgs a, double *__restrict__ out,
@@ -220,66 +282,15 @@ generic_blocked_kernel(const __grid_constant__ BlockedArgs a, double *__restrict
 
         for (int mid = 0; mid < a.mid_terms; ++mid)
         {
-            // product of the leading inputs that stay fixed while the innermost contracted index runs
-            double pre[R];
-#pragma unroll
-            for (int r = 0; r < R; ++r) pre[r] = 0.0;
-#pragma unroll
-            for (int v = 0; v < N_IN; ++v)
+            // one pass of the innermost contracted index, with the hoisted input count as a compile-time constant
+            switch (hoist)
             {
-                if (v < hoist)
-                {
-                    if ((a.dep_mask >> v) & 1u)
-                    {
-#pragma unroll
-                        for (int r = 0; r < R; ++r)
-                        {
-                            const double x = ins.p[v][off[v] + r * a.blk_in[v]];
-                            pre[r] = (v == 0) ? x : __dmul_rn(pre[r], x);
-                        }
-                    }
-                    else
-                    {
-                        const double x = ins.p[v][off[v]];
-#pragma unroll
-                        for (int r = 0; r < R; ++r) pre[r] = (v == 0) ? x : __dmul_rn(pre[r], x);
-                    }
-                }
-            }
-
-            int o[N_IN];
-#pragma unroll
-            for (int v = 0; v < N_IN; ++v) o[v] = off[v];
-            for (int i = 0; i < e_in; ++i)
-            {
-                double prod[R];
-#pragma unroll
-                for (int r = 0; r < R; ++r) prod[r] = pre[r];
-#pragma unroll
-                for (int v = 0; v < N_IN; ++v)
-                {
-                    if (v >= hoist)
-                    {
-                        if ((a.dep_mask >> v) & 1u)
-                        {
-#pragma unroll
-                            for (int r = 0; r < R; ++r)
-                            {
-                                const double x = ins.p[v][o[v] + r * a.blk_in[v]];
-                                prod[r] = (v == 0) ? x : __dmul_rn(prod[r], x);
-                            }
-                        }
-                        else
-                        {
-                            const double x = ins.p[v][o[v]];
-#pragma unroll
-                            for (int r = 0; r < R; ++r) prod[r] = (v == 0) ? x : __dmul_rn(prod[r], x);
-                        }
-                        if (n_contr > 0) o[v] += a.in_step[v][inner];
-                    }
-                }
-#pragma unroll
-                for (int r = 0; r < R; ++r) acc[r] = __dadd_rn(acc[r], prod[r]);
+                case 0: inner_pass<N_IN, R, 0>(a, ins, off, e_in, inner, acc); break;
+                case 1: inner_pass<N_IN, R, 1>(a, ins, off, e_in, inner, acc); break;
+                case 2: inner_pass<N_IN, R, (N_IN >= 2 ? 2 : N_IN)>(a, ins, off, e_in, inner, acc); break;
+                case 3: inner_pass<N_IN, R, (N_IN >= 3 ? 3 : N_IN)>(a, ins, off, e_in, inner, acc); break;
+                case 4: inner_pass<N_IN, R, (N_IN >= 4 ? 4 : N_IN)>(a, ins, off, e_in, inner, acc); break;
+                default: inner_pass<N_IN, R, N_IN>(a, ins, off, e_in, inner, acc); break;
             }
 
             // next combination of the other contracted indices (innermost of them fastest)
