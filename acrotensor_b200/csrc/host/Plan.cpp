@@ -344,8 +344,9 @@ bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
     s.bytes = io_bytes(k);
     s.flops = 2 * batch * m * n * kn;
     std::ostringstream note;
-    note << batch << " products of " << m << "x" << kn << " by " << kn << "x" << n
-         << ", persistent CTAs, 3-stage asynchronous bulk-copy ring, fp64 tensor cores (mma.sync m8n8k4)";
+    note << batch << " products of " << m << "x" << kn << " by " << kn << "x" << n;
+    if (m <= 16 && n <= 16 && kn <= 16) note << ", streaming tiles of matrices through shared memory (bulk copies), 4x1 strips per thread, no fused multiply-add";
+    else note << ", persistent CTAs, 3-stage asynchronous bulk-copy ring, fp64 tensor cores (mma.sync m8n8k4)";
     s.note = note.str();
     return true;
 }

@@ -178,13 +178,17 @@ batched_gemm_kernel(const GemmArgs a)
 
 extern "C" {
 
-int acro_b200_batched_gemm_supported(int m, int n, int k) { return (m == n && n == k && (m == 64 || m == 32)) ? 1 : 0; }
+int acro_b200_batched_gemm_supported(int m, int n, int k)
+{
+    return ((m == n && n == k && (m == 64 || m == 32)) || batched_gemm_small_supported(m, n, k)) ? 1 : 0;
+}
 
 int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int op, void *stream)
 {
     if (A == nullptr || B == nullptr || C == nullptr) return fail_invalid("acro_b200_batched_gemm: null argument");
     if (batch < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_batched_gemm: bad batch or operator");
-    if (!acro_b200_batched_gemm_supported(m, n, k)) return fail_unsupported("acro_b200_batched_gemm: only 64^3 and 32^3 are instantiated");
+    if (!acro_b200_batched_gemm_supported(m, n, k)) return fail_unsupported("acro_b200_batched_gemm: built for 64^3, 32^3 and every m, n, k <= 16");
+    if (batched_gemm_small_supported(m, n, k)) return batched_gemm_small_launch(A, B, C, batch, m, n, k, op, as_stream(stream));
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_batched_gemm");
 

@@ -33,6 +33,10 @@ inline int launch_status(const char *where)
     return status == cudaSuccess ? ACRO_B200_OK : fail_cuda(status, where);
 }
 
+// Streaming variant of batched_gemm for matrices up to 16 x 16 x 16 (batched_gemm_small.cu).
+bool batched_gemm_small_supported(int m, int n, int k);
+int batched_gemm_small_launch(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int op, cudaStream_t stream);
+
 __host__ __device__ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }

@@ -76,7 +76,8 @@ def test_batched_gemm_kernel(torch, batch, op, offset, n):
     ka, pa = to_dev(torch, a, offset)
     kb, pb = to_dev(torch, b)
     kc, pc = to_dev(torch, c0)
-    assert lib().acro_b200_batched_gemm_supported(n, n, n) == 1 and lib().acro_b200_batched_gemm_supported(n, n, 16) == 0
+    assert lib().acro_b200_batched_gemm_supported(n, n, n) == 1 and lib().acro_b200_batched_gemm_supported(n, n, 16) == 0 \
+        and lib().acro_b200_batched_gemm_supported(48, 48, 48) == 0
     check(lib().acro_b200_batched_gemm(pa, pb, pc, batch, n, n, n, op, None))
     status_ok()
     got = kc.cpu().numpy().reshape(c0.shape)
@@ -91,6 +92,32 @@ def test_batched_gemm_kernel(torch, batch, op, offset, n):
     ref = np.matmul(a, b)
     full = [ref, c0 + ref, c0 - ref][op]
     assert np.max(np.abs(got - full)) <= 1e-11
+
+
+@pytest.mark.parametrize("batch,m,n,k,op,offset", [
+    (1, 3, 3, 3, 0, 0), (1000, 3, 3, 3, 0, 0), (100001, 3, 3, 3, 0, 0), (4097, 4, 4, 4, 1, 0), (513, 8, 8, 8, 2, 0), (2050, 16, 16, 16, 0, 0),
+    (777, 16, 16, 16, 1, 1), (300, 5, 7, 3, 0, 0), (301, 1, 1, 1, 0, 0), (64, 2, 16, 9, 2, 1), (9000, 16, 1, 16, 0, 0), (2500, 12, 12, 12, 1, 0),
+    (33, 16, 15, 16, 0, 1)])
+def test_small_batched_gemm_kernel_is_bit_identical(torch, batch, m, n, k, op, offset):
+    """Matrices up to 16 x 16 x 16: the streaming variant, same operation order as the reference's CPU executor."""
+    rng = np.random.default_rng(batch + m)
+    a, b = rng.standard_normal((batch, m, k)), rng.standard_normal((batch, k, n))
+    c0 = rng.random((batch, m, n))
+    ka, pa = to_dev(torch, a, offset)
+    kb, pb = to_dev(torch, b)
+    kc, pc = to_dev(torch, c0, offset)
+    assert lib().acro_b200_batched_gemm_supported(m, n, k) == 1 and lib().acro_b200_batched_gemm_supported(m, 17, k) == 0
+    check(lib().acro_b200_batched_gemm(pa, pb, pc, batch, m, n, k, op, None))
+    status_ok()
+    got = kc[offset:].cpu().numpy().reshape(c0.shape)
+    if op == 2:
+        prod = np.zeros_like(c0)
+        oracle.contract("port", "C_e_i_j = A_e_i_k B_e_k_j", prod, a, b)
+        expect = c0 - prod
+    else:
+        expect = c0.copy()
+        oracle.contract("port", "C_e_i_j %s A_e_i_k B_e_k_j" % ["=", "+="][op], expect, a, b)
+    assert np.array_equal(got, expect)
 
 
 def run_chain_oracle(b, u, w):
