@@ -174,20 +174,205 @@ batched_gemm_kernel(const GemmArgs a)
     }
 }
 
+
+// ------------------------------------------------------------------ any m, n, k up to N
+// The same ring and the same warp tiling for matrices that do not fill the N x N slots: the slots are
+// zeroed once, every element's entries are copied to the top-left corner of its slots (16-byte cp.async
+// when rows are 16-byte multiples on 16-byte boundaries, else 8-byte), so the padding rows and columns
+// stay zero and add nothing; the contracted extent is walked in steps of four up to its padded value,
+// accumulator tiles that lie entirely outside C are skipped, and only the valid entries of C are stored.
+struct PaddedArgs
+{
+    const double *A;
+    const double *B;
+    double *C;
+    int64_t batch;
+    int m, n, k, op;
+    int *wait_flag;
+    int wide;        // rows of A and B are 16-byte multiples on 16-byte boundaries: 16-byte copies
+};
+
+template <int N>
+__device__ __forceinline__ void issue_padded_load(Smem<N> &s, const PaddedArgs &a, int64_t e, int stage)
+{
+    constexpr int LD = Smem<N>::LD;
+    const int tid = threadIdx.x;
+    const double *ga = a.A + e * a.m * a.k, *gb = a.B + e * a.k * a.n;
+    if (a.wide)
+    {
+        const int ca = a.k / 2, cb = a.n / 2;          // 16-byte chunks per row
+        int col = tid % ca, row = tid / ca;
+        const int sc = NT % ca, sr = NT / ca;
+        for (int c = tid; row < a.m; c += NT)
+        {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&s.A[stage][row * LD + col * 2])), "l"(ga + c * 2) : "memory");
+            col += sc;
+            if (col >= ca) { col -= ca; ++row; }
+            row += sr;
+        }
+        col = tid % cb, row = tid / cb;
+        const int tc = NT % cb, tr = NT / cb;
+        for (int c = tid; row < a.k; c += NT)
+        {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&s.B[stage][row * LD + col * 2])), "l"(gb + c * 2) : "memory");
+            col += tc;
+            if (col >= cb) { col -= cb; ++row; }
+            row += tr;
+        }
+    }
+    else
+    {
+        int col = tid % a.k, row = tid / a.k;
+        const int sc = NT % a.k, sr = NT / a.k;
+        for (int c = tid; row < a.m; c += NT)
+        {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_addr(&s.A[stage][row * LD + col])), "l"(ga + c) : "memory");
+            col += sc;
+            if (col >= a.k) { col -= a.k; ++row; }
+            row += sr;
+        }
+        col = tid % a.n, row = tid / a.n;
+        const int tc = NT % a.n, tr = NT / a.n;
+        for (int c = tid; row < a.k; c += NT)
+        {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_addr(&s.B[stage][row * LD + col])), "l"(gb + c) : "memory");
+            col += tc;
+            if (col >= a.n) { col -= a.n; ++row; }
+            row += tr;
+        }
+    }
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&s.full[stage])) : "memory");
+}
+
+template <int N>
+__global__ void __launch_bounds__(NT, N == 64 ? 1 : 4)
+batched_gemm_padded_kernel(const PaddedArgs a)
+{
+    constexpr int LD = Smem<N>::LD;
+    constexpr int MT = N / 32, NTL = N / 16;
+    extern __shared__ __align__(128) unsigned char raw[];
+    Smem<N> &s = *reinterpret_cast<Smem<N> *>(raw);
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int m0 = (warp >> 1) * (N / 4), n0 = (warp & 1) * (N / 2);
+    const int m = a.m, n = a.n;
+    const int k4 = (a.k + 3) & ~3;
+
+    if (tid == 0)
+    {
+        for (int i = 0; i < STAGES; ++i)
+        {
+            mbar_init(&s.full[i], NT);
+            mbar_init(&s.empty[i], NT);
+        }
+        fence_mbar_init();
+    }
+    for (int i = tid; i < STAGES * Smem<N>::MAT; i += NT)
+    {
+        (&s.A[0][0])[i] = 0.0;
+        (&s.B[0][0])[i] = 0.0;
+    }
+    __syncthreads();
+
+    int64_t e = blockIdx.x;
+    if (e < a.batch) issue_padded_load(s, a, e, 0);
+
+    int64_t it = 0;
+    for (; e < a.batch; e += gridDim.x, ++it)
+    {
+        const int stage = static_cast<int>(it % STAGES);
+        const int64_t nxt = e + gridDim.x;
+        if (nxt < a.batch)
+        {
+            const int ns = static_cast<int>((it + 1) % STAGES);
+            const int64_t use = (it + 1) / STAGES;
+            if (use > 0 && !mbar_wait(&s.empty[ns], static_cast<uint32_t>((use - 1) & 1))) atomicExch(a.wait_flag, 1);
+            issue_padded_load(s, a, nxt, ns);
+        }
+        if (!mbar_wait(&s.full[stage], static_cast<uint32_t>((it / STAGES) & 1))) atomicExch(a.wait_flag, 1);
+
+        const double *sa = s.A[stage];
+        const double *sb = s.B[stage];
+        double c[MT][NTL][2];
+        bool row_live[MT], col_live[NTL];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) row_live[mt] = m0 + mt * 8 < m;
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt) col_live[nt] = n0 + nt * 8 < n;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NTL; ++nt) c[mt][nt][0] = c[mt][nt][1] = 0.0;
+
+        if (row_live[0] && col_live[0])
+        {
+            for (int k0 = 0; k0 < k4; k0 += 4)
+            {
+                double af[MT], bf[NTL];
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) af[mt] = sa[(m0 + mt * 8 + g) * LD + k0 + t];
+#pragma unroll
+                for (int nt = 0; nt < NTL; ++nt) bf[nt] = sb[(k0 + t) * LD + n0 + nt * 8 + g];
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < NTL; ++nt)
+                    {
+                        if (row_live[mt] && col_live[nt]) dmma_m8n8k4(c[mt][nt], af[mt], bf[nt]);
+                    }
+            }
+        }
+        mbar_arrive(&s.empty[stage]);   // this thread no longer reads the slot
+
+        double *gc = a.C + e * m * n;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NTL; ++nt)
+            {
+                const int i = m0 + mt * 8 + g, j = n0 + nt * 8 + 2 * t;
+                if (i >= m) continue;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                {
+                    if (j + h >= n) continue;
+                    double *dst = gc + i * n + j + h;
+                    double v = c[mt][nt][h];
+                    if (a.op == ACRO_B200_OP_ADD) v += *dst;
+                    else if (a.op == ACRO_B200_OP_SUB) v = *dst - v;
+                    __stcs(dst, v);
+                }
+            }
+    }
+}
+
+template <int N>
+int launch_padded(const PaddedArgs &args, int sms, cudaStream_t stream)
+{
+    const size_t smem = sizeof(Smem<N>);
+    cudaError_t status = cudaFuncSetAttribute(batched_gemm_padded_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_batched_gemm (shared memory opt-in)");
+    int64_t grid = static_cast<int64_t>(sms) * (N == 64 ? 1 : 4);
+    if (grid > args.batch) grid = args.batch;
+    batched_gemm_padded_kernel<N><<<static_cast<int>(grid), NT, smem, stream>>>(args);
+    return launch_status("acro_b200_batched_gemm (padded)");
+}
+
 }
 
 extern "C" {
 
 int acro_b200_batched_gemm_supported(int m, int n, int k)
 {
-    return ((m == n && n == k && (m == 64 || m == 32)) || batched_gemm_small_supported(m, n, k)) ? 1 : 0;
+    return (m >= 1 && n >= 1 && k >= 1 && m <= 64 && n <= 64 && k <= 64) ? 1 : 0;
 }
 
 int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int op, void *stream)
 {
     if (A == nullptr || B == nullptr || C == nullptr) return fail_invalid("acro_b200_batched_gemm: null argument");
     if (batch < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_batched_gemm: bad batch or operator");
-    if (!acro_b200_batched_gemm_supported(m, n, k)) return fail_unsupported("acro_b200_batched_gemm: built for 64^3, 32^3 and every m, n, k <= 16");
+    if (!acro_b200_batched_gemm_supported(m, n, k)) return fail_unsupported("acro_b200_batched_gemm: m, n, k must be in 1..64");
     if (batched_gemm_small_supported(m, n, k)) return batched_gemm_small_launch(A, B, C, batch, m, n, k, op, as_stream(stream));
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_batched_gemm");
@@ -202,6 +387,22 @@ int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t 
     if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_batched_gemm (status flag)");
     args.async_copy = (aligned16(A) && aligned16(B)) ? 1 : 0;
 
+    if (!(m == n && n == k && (m == 64 || m == 32)))
+    {
+        PaddedArgs pa;
+        pa.A = A;
+        pa.B = B;
+        pa.C = C;
+        pa.batch = batch;
+        pa.m = m;
+        pa.n = n;
+        pa.k = k;
+        pa.op = op;
+        pa.wait_flag = args.wait_flag;
+        pa.wide = (aligned16(A) && aligned16(B) && k % 2 == 0 && n % 2 == 0 && (m * k) % 2 == 0 && (k * n) % 2 == 0) ? 1 : 0;
+        const int largest = m > n ? (m > k ? m : k) : (n > k ? n : k);
+        return largest <= 32 ? launch_padded<32>(pa, sms, as_stream(stream)) : launch_padded<64>(pa, sms, as_stream(stream));
+    }
     auto kernel = m == 64 ? batched_gemm_kernel<64> : batched_gemm_kernel<32>;
     const size_t smem = m == 64 ? sizeof(Smem<64>) : sizeof(Smem<32>);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

@@ -223,10 +223,11 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
 
 /*
  * batched_gemm:  C[e,i,j] (op)= sum_{k} A[e,i,k] * B[e,k,j]  for a batch of dense row-major
- * matrices ("C_e_i_j = A_e_i_k B_e_k_j").  Built for m = n = k = 64 and 32 (persistent CTAs,
- * three-stage asynchronous bulk-copy ring for A_e and B_e, fp64 tensor cores) and for every
- * m, n, k <= 16 (HBM-bound: tiles of matrices streamed through shared memory by bulk copies,
- * separate multiply and add in ascending k, bit-identical to the reference's CPU executor).
+ * matrices ("C_e_i_j = A_e_i_k B_e_k_j"), any m, n, k in 1..64.  64^3 and 32^3: persistent CTAs,
+ * three-stage asynchronous copy ring for A_e and B_e, fp64 tensor cores; other sizes above 16 use
+ * the same kernel with the matrices zero-padded on chip to 32 or 64.  Every m, n, k <= 16 is
+ * HBM-bound: tiles of matrices streamed through shared memory by bulk copies, separate multiply
+ * and add in ascending k, bit-identical to the reference's CPU executor.
  * HBM traffic 8*(mk + kn + mn) bytes and 2mnk flops per element.  Replaces the generated kernel
  * (scalar DFMA from global memory, no tiling, exec/CudaExecutor.cpp:520-604).
  */

@@ -76,8 +76,7 @@ def test_batched_gemm_kernel(torch, batch, op, offset, n):
     ka, pa = to_dev(torch, a, offset)
     kb, pb = to_dev(torch, b)
     kc, pc = to_dev(torch, c0)
-    assert lib().acro_b200_batched_gemm_supported(n, n, n) == 1 and lib().acro_b200_batched_gemm_supported(n, n, 16) == 0 \
-        and lib().acro_b200_batched_gemm_supported(48, 48, 48) == 0
+    assert lib().acro_b200_batched_gemm_supported(n, n, n) == 1 and lib().acro_b200_batched_gemm_supported(n, n, 65) == 0
     check(lib().acro_b200_batched_gemm(pa, pb, pc, batch, n, n, n, op, None))
     status_ok()
     got = kc.cpu().numpy().reshape(c0.shape)
@@ -106,7 +105,7 @@ def test_small_batched_gemm_kernel_is_bit_identical(torch, batch, m, n, k, op, o
     ka, pa = to_dev(torch, a, offset)
     kb, pb = to_dev(torch, b)
     kc, pc = to_dev(torch, c0, offset)
-    assert lib().acro_b200_batched_gemm_supported(m, n, k) == 1 and lib().acro_b200_batched_gemm_supported(m, 17, k) == 0
+    assert lib().acro_b200_batched_gemm_supported(m, n, k) == 1 and lib().acro_b200_batched_gemm_supported(m, 0, k) == 0
     check(lib().acro_b200_batched_gemm(pa, pb, pc, batch, m, n, k, op, None))
     status_ok()
     got = kc[offset:].cpu().numpy().reshape(c0.shape)
@@ -118,6 +117,28 @@ def test_small_batched_gemm_kernel_is_bit_identical(torch, batch, m, n, k, op, o
         expect = c0.copy()
         oracle.contract("port", "C_e_i_j %s A_e_i_k B_e_k_j" % ["=", "+="][op], expect, a, b)
     assert np.array_equal(got, expect)
+
+
+@pytest.mark.parametrize("batch,m,n,k,op,offset", [
+    (1, 27, 27, 27, 0, 0), (500, 27, 27, 27, 0, 0), (301, 27, 27, 27, 1, 1), (64, 20, 33, 17, 0, 0), (40, 64, 64, 48, 2, 0), (90, 17, 64, 5, 0, 0),
+    (75, 33, 1, 64, 0, 1), (130, 48, 48, 48, 1, 0), (55, 18, 24, 30, 0, 0), (33, 32, 32, 31, 0, 0), (20, 63, 63, 63, 0, 1)])
+def test_padded_batched_gemm_kernel(torch, batch, m, n, k, op, offset):
+    """Sizes between 17 and 64 that do not fill the 32- or 64-wide slots: zero-padded on chip, fp64 tensor cores."""
+    rng = np.random.default_rng(batch + m + k)
+    a, b = rng.standard_normal((batch, m, k)), rng.standard_normal((batch, k, n))
+    c0 = rng.random((batch, m, n))
+    ka, pa = to_dev(torch, a, offset)
+    kb, pb = to_dev(torch, b)
+    kc, pc = to_dev(torch, c0, offset)
+    assert lib().acro_b200_batched_gemm_supported(m, n, k) == 1
+    check(lib().acro_b200_batched_gemm(pa, pb, pc, batch, m, n, k, op, None))
+    status_ok()
+    got = kc[offset:].cpu().numpy().reshape(c0.shape)
+    prod, mags = np.zeros_like(c0), np.zeros_like(c0)
+    oracle.contract("port", "C_e_i_j = A_e_i_k B_e_k_j", prod, a, b)
+    oracle.contract("port", "C_e_i_j = A_e_i_k B_e_k_j", mags, np.abs(a), np.abs(b))
+    expect = [prod, c0 + prod, c0 - prod][op]
+    assert oracle.parity_error(got, expect, mags + np.abs(c0)) <= TOL
 
 
 def run_chain_oracle(b, u, w):
