@@ -161,6 +161,16 @@ void B200Executor::Run(std::vector<Tensor *> &outputs, std::vector<std::vector<T
                           "sumfact_mass");
                 break;
             }
+            case plan::Family::InvariantGemm:
+            {
+                const double *ptrs[ACRO_B200_MAX_INPUTS];
+                for (std::size_t i = 1; i < ins.size(); ++i) ptrs[i - 1] = ins[i]->GetDeviceData();
+                check_abi(acro_b200_generic_launch(&s.generic, Scratch, ptrs, nullptr, 0, stream), "generic_launch (invariant product)");
+                check_abi(acro_b200_gemm(ins[0]->GetDeviceData(), Scratch, out->GetDeviceData(), s.rows, s.sizes[1], s.sizes[0], s.sizes[0],
+                                         s.sizes[2], s.sizes[1], s.op, stream),
+                          "gemm");
+                break;
+            }
             default:
                 ACROBATIC_ASSERT(false, "Planned a kernel family that is not built into this library.");
         }

@@ -3,6 +3,7 @@
 #include "Plan.hpp"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <sstream>
@@ -309,6 +310,100 @@ bool plan_rank1_gemm(DimensionedKernel &k, int ki, Step &s)
     return true;
 }
 
+// ---------------------------------------------------------------- invariant_gemm
+// Out_e_X = (product of batch-invariant inputs) In_e_Q: exactly one input carries the batch index e, in
+// front, and its other indices are exactly the contracted ones.  The invariant inputs are multiplied
+// out into P[Q x X] by the generic kernel (left to right, as written), then Out[e, X] = sum_Q In[e, Q] P[Q, X]
+// is one GEMM with the batch as its row dimension.
+bool plan_invariant_gemm(DimensionedKernel &k, int ki, Step &s)
+{
+    const Names out = k.OutputVar.IndexNames;
+    const int n_in = k.GetNumInputVars();
+    if (out.size() < 2 || !distinct(out) || n_in < 2 || n_in > ACRO_B200_MAX_INPUTS || k.ContractionIndexNames.empty()) return false;
+    const std::string e = out[0];
+    int batched = -1;
+    for (int vari = 0; vari < n_in; ++vari)
+    {
+        const Names idx = indices_of(k, vari);
+        const bool has_e = std::find(idx.begin(), idx.end(), e) != idx.end();
+        if (!has_e) continue;
+        if (batched >= 0 || idx[0] != e || !distinct(idx)) return false;
+        batched = vari;
+    }
+    if (batched < 0) return false;
+    const Names q_full = indices_of(k, batched);
+    const Names q(q_full.begin() + 1, q_full.end());
+    Names contracted = k.ContractionIndexNames, q_sorted = q;
+    std::sort(contracted.begin(), contracted.end());
+    std::sort(q_sorted.begin(), q_sorted.end());
+    if (q_sorted != contracted) return false;
+    const Names x(out.begin() + 1, out.end());
+    if (q.size() + x.size() > ACRO_B200_MAX_LOOPS) return false;
+
+    const std::int64_t elements = extent_of(k, e);
+    std::int64_t kk = 1, nn = 1;
+    for (const std::string &idx : q) kk *= extent_of(k, idx);
+    for (const std::string &idx : x) nn *= extent_of(k, idx);
+    // worth a tensor-core GEMM, and P small enough to rebuild on every call
+    if (elements < 64 || nn < 16 || kk < 4 || kk * nn > (std::int64_t(1) << 26)) return false;
+    if (elements * nn * kk < (std::int64_t(1) << 22)) return false;
+
+    s = Step();
+    s.family = Family::InvariantGemm;
+    s.kernels = {ki};
+    s.out.ki = ki;
+    s.op = op_code(k);
+    s.rows = elements;
+    s.sizes[0] = static_cast<int>(kk);
+    s.sizes[1] = static_cast<int>(nn);
+
+    // P[q..., x...] = product of the invariant inputs, in the order they are written
+    Names loops = concat(q, x);
+    acro_b200_generic_desc &g = s.generic;
+    std::memset(&g, 0, sizeof g);
+    g.n_loops = g.n_outer = static_cast<int>(loops.size());
+    g.n_inputs = n_in - 1;
+    g.op = ACRO_B200_OP_ASSIGN;
+    // rows of P padded to an even length: every row then starts on a 16-byte boundary
+    const std::int64_t ldp = nn + (nn & 1);
+    s.sizes[2] = static_cast<int>(ldp);
+    std::int64_t stride = 1;
+    for (int l = g.n_loops - 1; l >= 0; --l)
+    {
+        g.extent[l] = extent_of(k, loops[l]);
+        g.out_step[l] = stride;
+        stride *= g.extent[l];
+        if (l == static_cast<int>(q.size())) stride = ldp;      // the first output index closes a row of P
+    }
+    TensorRef br;
+    br.ki = ki;
+    br.vari = batched;
+    s.ins.push_back(br);
+    int slot = 0;
+    for (int vari = 0; vari < n_in; ++vari)
+    {
+        if (vari == batched) continue;
+        const Names idx = indices_of(k, vari);
+        for (int d = 0; d < static_cast<int>(idx.size()); ++d)
+        {
+            const int l = static_cast<int>(std::find(loops.begin(), loops.end(), idx[d]) - loops.begin());
+            g.in_step[slot][l] += k.GetVarDimStride64(vari, d);
+        }
+        TensorRef r;
+        r.ki = ki;
+        r.vari = vari;
+        s.ins.push_back(r);
+        ++slot;
+    }
+    s.bytes = io_bytes(k);
+    s.flops = 2 * elements * kk * nn;   // GEMM form
+    std::ostringstream note;
+    note << "batch-invariant inputs multiplied out into P[" << kk << " x " << nn << "], then GEMM [" << elements << " x " << kk
+         << "] x P on the fp64 tensor cores (mma.sync m8n8k4)";
+    s.note = note.str();
+    return true;
+}
+
 // ---------------------------------------------------------------- batched_gemm
 // C_e_i_j = A_e_i_k B_e_k_j (either operand order).
 bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
@@ -468,10 +563,14 @@ bool plan_sumfact_mass(DimensionedMultiKernel &mk, Step &s)
 Step plan_single(DimensionedKernel &k, int ki)
 {
     Step s;
+    // debugging aid: ACRO_B200_ONLY_GENERIC=1 in the environment plans every kernel on the generic family
+    const char *only_generic = std::getenv("ACRO_B200_ONLY_GENERIC");
+    if (only_generic != nullptr && only_generic[0] == '1') return plan_generic(k, ki);
     if (plan_reduce_batch(k, ki, s)) return s;
     if (plan_pointwise_sym(k, ki, s)) return s;
     if (plan_rank1_gemm(k, ki, s)) return s;
     if (plan_batched_gemm(k, ki, s)) return s;
+    if (plan_invariant_gemm(k, ki, s)) return s;
     return plan_generic(k, ki);
 }
 
@@ -487,6 +586,7 @@ const char *FamilyName(Family f)
         case Family::Rank1Gemm: return "rank1_gemm";
         case Family::BatchedGemm: return "batched_gemm";
         case Family::SumfactMass: return "sumfact_mass";
+        case Family::InvariantGemm: return "invariant_gemm";
     }
     return "?";
 }
@@ -517,6 +617,10 @@ Program BuildProgram(DimensionedMultiKernel &mk, bool allow_elision)
         if (s.family == Family::Generic)
         {
             p.scratch_bytes = std::max(p.scratch_bytes, acro_b200_generic_scratch_bytes(&s.generic));
+        }
+        if (s.family == Family::InvariantGemm)
+        {
+            p.scratch_bytes = std::max(p.scratch_bytes, static_cast<std::size_t>(s.sizes[0]) * static_cast<std::size_t>(s.sizes[2]) * sizeof(double));
         }
     }
     return p;

@@ -23,7 +23,8 @@ enum class Family
     PointwiseSym,
     Rank1Gemm,
     BatchedGemm,
-    SumfactMass
+    SumfactMass,
+    InvariantGemm
 };
 
 const char *FamilyName(Family f);

@@ -330,7 +330,7 @@ BlockedPlan blocked_plan(const acro_b200_generic_desc &d)
 {
     BlockedPlan p;
     const int n_contr = d.n_loops - d.n_outer;
-    if (d.n_inputs < 2 || d.n_inputs > kBlockedMaxInputs || n_contr < 1) return p;
+    if (d.n_inputs < 2 || d.n_inputs > kBlockedMaxInputs || n_contr < 0) return p;      // entry-wise products (no contraction) too
     int64_t outer_points = 1, terms = 1;
     for (int l = 0; l < d.n_loops; ++l) (l < d.n_outer ? outer_points : terms) *= d.extent[l];
     if (terms >= 0x7fffffffLL) return p;
@@ -352,7 +352,7 @@ BlockedPlan blocked_plan(const acro_b200_generic_desc &d)
     // ones read with unit stride across a warp), and rather an inner loop than an outer one.
     const int inner = d.n_loops - 1;
     int hoist = 0;
-    while (hoist < d.n_inputs && d.in_step[hoist][inner] == 0) ++hoist;
+    while (n_contr > 0 && hoist < d.n_inputs && d.in_step[hoist][inner] == 0) ++hoist;
     double best = 0.0;
     for (int v = 0; v < d.n_inputs; ++v) best += v < hoist ? 1.0 / static_cast<double>(d.extent[inner]) : 1.0;
     static const int kEntries[4] = {4, 5, 3, 2};
@@ -611,7 +611,7 @@ extern "C" int acro_b200_generic_launch(const acro_b200_generic_desc *desc, doub
         a.n_loops = desc->n_loops;
         a.op = desc->op;
         const int inner = desc->n_loops - 1;
-        a.mid_terms = static_cast<int>(terms / desc->extent[inner]);
+        a.mid_terms = desc->n_loops > desc->n_outer ? static_cast<int>(terms / desc->extent[inner]) : 1;
         for (int l = 0; l < desc->n_loops; ++l)
         {
             a.extent[l] = static_cast<int>(l == bp.loop ? desc->extent[l] / bp.entries : desc->extent[l]);
@@ -624,7 +624,7 @@ extern "C" int acro_b200_generic_launch(const acro_b200_generic_desc *desc, doub
         {
             a.blk_in[v] = static_cast<int>(a.extent[bp.loop] * desc->in_step[v][bp.loop]);
             if (desc->in_step[v][bp.loop] != 0) a.dep_mask |= 1u << v;
-            leading = leading && desc->in_step[v][inner] == 0;
+            leading = leading && desc->n_loops > desc->n_outer && desc->in_step[v][inner] == 0;
             if (leading) a.hoist = v + 1;
         }
         const int64_t coarse = outer_points / bp.entries;

@@ -587,15 +587,29 @@ def run_ops(args):
         per_op["sumfact_mass_p%d_q%d" % (p, q)] = entry(timed(step), Ec * 8 * (2 * p ** 3 + q ** 3), "%d elements, six stages fused" % Ec)
         del t, spare
 
-    # finite-element assembly strings of the reference's tests on the generic kernel (register-blocked variant)
-    Eg = max(1, int(65536 * args.scale))
-    B, D = dev_tensor((4, 4), -1, 1), dev_tensor((Eg, 4, 4))
-    Mm = torch.empty((Eg, 4, 4, 4, 4), device="cuda", dtype=torch.float64)
-    TB, TDd, TM = bind(B), bind(D), bind(Mm)
-    kernel = "M_e_i1_i2_j1_j2=B_k1_i1 B_k1_j1 B_k2_i2 B_k2_j2 D_e_k1_k2"
-    per_op["generic_mass2d_assembly"] = entry(timed(lambda: te(kernel, TM, TB, TB, TB, TB, TDd)), Eg * 8 * (256 + 16),
-                                              "%d elements, 16 terms per entry; %s" % (Eg, te.GetImplementation(kernel, TM, TB, TB, TB, TB, TDd).split("|")[-1].strip()))
-    del B, D, Mm, TB, TDd, TM
+    # finite-element assembly strings of the reference's tests: one batched input times batch-invariant factors,
+    # planned as "multiply the invariant factors out, then one tensor-core GEMM"
+    assembly = [
+        ("assembly_mass2d", "M_e_i1_i2_j1_j2=B_k1_i1 B_k1_j1 B_k2_i2 B_k2_j2 D_e_k1_k2", ["M", "B", "B", "B", "B", "D"],
+         lambda n: {"M": (n, 4, 4, 4, 4), "B": (4, 4), "D": (n, 4, 4)}, 65536),
+        ("assembly_stiffness3d", "S_e_i1_i2_i3_j1_j2_j3 = Bt1_i1_j1_k1_m_n Bt2_i2_j2_k2_m_n Bt3_i3_j3_k3_m_n D_e_k1_k2_k3_m_n",
+         ["S", "Bt1", "Bt2", "Bt3", "D"],
+         lambda n: {"S": (n, 5, 5, 5, 5, 5, 5), "Bt1": (5, 5, 5, 3, 3), "Bt2": (5, 5, 5, 3, 3), "Bt3": (5, 5, 5, 3, 3), "D": (n, 5, 5, 5, 3, 3)}, 256),
+        ("assembly_mass_q125", "M_e_i_j = W_e_q B_q_i B_q_j", ["M", "W", "B", "B"],
+         lambda n: {"M": (n, 64, 64), "W": (n, 125), "B": (125, 64)}, 32768),
+    ]
+    for key, kernel, names, shapes_of, full in assembly:
+        n = max(64, int(full * args.scale))
+        dev = {k: dev_tensor(v, -1, 1) for k, v in shapes_of(n).items()}
+        t = {k: bind(v) for k, v in dev.items()}
+        operands = [t[k] for k in names]
+        plan_line = [l for l in te.GetImplementation(kernel, *operands).splitlines() if l.startswith("step 0")][0]
+        ms_a = timed(lambda: te(kernel, *operands))
+        flops = float(plan_line.split("flops=")[1].split()[0])
+        e = entry(ms_a, float(plan_line.split("bytes=")[1].split()[0]), "%d elements; %s" % (n, plan_line.split("family=")[1].split()[0]))
+        e["TFLOPps"] = round(flops / ms_a * 1e-9, 2)
+        per_op[key] = e
+        del dev, t, operands
 
     ms, nbytes = headline
     print(json.dumps({"metric": "batch_inv_det_throughput", "value": round(nbytes / ms * 1e-6, 1), "unit": "GB/s", "n_gpus": 1,

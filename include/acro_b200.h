@@ -236,6 +236,18 @@ int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t 
                            int op, void *stream);
 
 /*
+ * gemm:  C[M x N] (op)= A[M x K] * P[K x N], row-major fp64 with leading dimensions lda, ldp, ldc (in
+ * doubles), on the fp64 tensor cores: 64 x 64 tiles, K walked in slabs of 64 through a three-slot
+ * asynchronous copy ring.  The engine uses it for contractions in which exactly one input carries the
+ * batch index and all its other indices are contracted (assembly strings such as
+ * "M_e_i1_i2_j1_j2 = B_k1_i1 B_k1_j1 B_k2_i2 B_k2_j2 D_e_k1_k2"): the batch-invariant inputs are first
+ * multiplied out into P by acro_b200_generic_launch.  The reference's generator runs these as scalar
+ * loops per output entry (exec/CudaExecutor.cpp:520-604).
+ */
+int acro_b200_gemm(const double *A, const double *P, double *C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldp,
+                   int64_t ldc, int op, void *stream);
+
+/*
  * sumfact_mass: the six-stage sum-factorised 3D mass operator as ONE kernel,
  *   V_e_i1_i2_i3 = sum B_k3_i3 B_k2_i2 B_k1_i1 W_e_k1_k2_k3 (sum B_k1_j1 B_k2_j2 B_k3_j3 U_e_j1_j2_j3),
  * evaluated stage by stage (contract i3, i2, i1, scale by W, contract k1, k2, k3) with every

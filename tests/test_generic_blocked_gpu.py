@@ -11,6 +11,12 @@ import gpu_util as gu
 
 pytestmark = pytest.mark.gpu
 
+
+@pytest.fixture(autouse=True)
+def only_the_generic_family(monkeypatch):
+    # some of these strings would otherwise be planned on a specialised family (they are assembly strings)
+    monkeypatch.setenv("ACRO_B200_ONLY_GENERIC", "1")
+
 BLOCKED_CASES = [
     # the reference's 2D mass assembly string (unittest/kernel/test_TensorEngine.cpp:232-300) at scale:
     # two leading inputs are hoisted out of the k2 loop, four entries per thread
@@ -30,6 +36,8 @@ BLOCKED_CASES = [
     # three entries per thread (3^11 rows), and two (2 * 100003 rows)
     ("three_per_thread", [("A_e_i = B_e_i_k C_k", "A", ["B", "C"])], {"A": (177147, 2), "B": (177147, 2, 7), "C": (7,)}, False),
     ("two_per_thread", [("A_e = B_e_k C_k D_k", "A", ["B", "C", "D"])], {"A": (200006,), "B": (200006, 5), "C": (5,), "D": (5,)}, False),
+    # entry-wise products without any contraction (what builds the invariant factor of an assembly string)
+    ("outer_product", [("P_a_b_c = X_a_c Y_b_c Z_c", "P", ["X", "Y", "Z"])], {"P": (300, 400, 6), "X": (300, 6), "Y": (400, 6), "Z": (6,)}, False),
     # a leading input without any contracted index, and a diagonal read
     ("hoisted_scale", [("A_i_j = S_i B_j_k C_k_k", "A", ["S", "B", "C"])], {"A": (640, 640), "S": (640,), "B": (640, 9), "C": (9, 9)}, False),
 ]

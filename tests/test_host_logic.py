@@ -220,3 +220,24 @@ def test_workload_byte_and_flop_models():
         assert set(ins) == set(w.names("in"))
         for k in ins:
             assert ins[k].shape == w.shapes(3)[k] and np.array_equal(ins[k], again[k])
+
+
+def test_assembly_strings_are_planned_as_a_gemm_only_at_scale(monkeypatch):
+    kernel = "M_e_i1_i2_j1_j2=B_k1_i1 B_k1_j1 B_k2_i2 B_k2_j2 D_e_k1_k2"
+
+    def plan(elements):
+        B, D = ab.Tensor(4, 4, hdata=np.zeros((4, 4))), ab.Tensor(elements, 4, 4, hdata=np.zeros((elements, 4, 4)))
+        M = ab.Tensor(elements, 4, 4, 4, 4, hdata=np.zeros((elements, 4, 4, 4, 4)))
+        return ab.TensorEngine("Cuda").GetImplementation(kernel, M, B, B, B, B, D)
+
+    assert "family=generic" in plan(10)
+    big = plan(5000)
+    assert "family=invariant_gemm" in big and "P[16 x 256]" in big and "scratch: 32768 bytes" in big
+    monkeypatch.setenv("ACRO_B200_ONLY_GENERIC", "1")
+    assert "family=generic" in plan(5000)
+    # two batched inputs, or a batched input with an uncontracted index: not this family
+    monkeypatch.delenv("ACRO_B200_ONLY_GENERIC")
+    A = ab.Tensor(5000, 4, 4, hdata=np.zeros((5000, 4, 4)))
+    G = ab.Tensor(4, 4, hdata=np.zeros((4, 4)))
+    U = ab.Tensor(5000, 4, 4, hdata=np.zeros((5000, 4, 4)))
+    assert "invariant_gemm" not in ab.TensorEngine("Cuda").GetImplementation("U_e_k1_k2 = G_k1_i1 A_e_i1_k2", U, G, A)
