@@ -241,3 +241,19 @@ def test_assembly_strings_are_planned_as_a_gemm_only_at_scale(monkeypatch):
     G = ab.Tensor(4, 4, hdata=np.zeros((4, 4)))
     U = ab.Tensor(5000, 4, 4, hdata=np.zeros((5000, 4, 4)))
     assert "invariant_gemm" not in ab.TensorEngine("Cuda").GetImplementation("U_e_k1_k2 = G_k1_i1 A_e_i1_k2", U, G, A)
+
+
+def test_entry_points_validate_their_arguments_before_touching_a_device():
+    """Argument errors are reported as ACRO_B200_EINVAL / EUNSUPPORTED with a message, also on a machine without a GPU."""
+    from acrotensor_b200._lib import lib
+    buf = (ctypes.c_double * 64)()
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert lib().acro_b200_gemm(None, p, p, 4, 4, 4, 4, 4, 4, 0, None) == _lib.EINVAL
+    assert lib().acro_b200_gemm(p, p, p, 4, 4, 4, 3, 4, 4, 0, None) == _lib.EINVAL          # lda < K
+    assert lib().acro_b200_gemm(p, p, p, 4, 4, 4, 4, 4, 4, 3, None) == _lib.EINVAL          # unknown operator
+    assert b"acro_b200_gemm" in lib().acro_b200_last_error()
+    assert lib().acro_b200_batched_gemm(p, p, p, 1, 65, 4, 4, 0, None) == _lib.EUNSUPPORTED
+    assert lib().acro_b200_batched_gemm(p, p, p, 0, 4, 4, 4, 0, None) == _lib.EINVAL
+    assert lib().acro_b200_rank1_gemm(p, p, p, p, 8, 65, 4, 4, 0, None) == _lib.EUNSUPPORTED
+    assert lib().acro_b200_sumfact_mass(p, p, p, p, 8, 6, 7, None) == _lib.EUNSUPPORTED
+    assert lib().acro_b200_halo_exchange_sum(None, p, None) == _lib.EINVAL
