@@ -658,7 +658,7 @@ class CpuSample:
         return total_bytes / full_seconds * 1e-9, full_seconds, detail, kind
 
 
-def cpu_sample_for_budget(workloads, args, threads, seconds_per_pass):
+def cpu_sample_for_seconds(workloads, args, threads, seconds_per_pass):
     """Calibrates on a small sample, then sizes the sample so that one pass takes about
     `seconds_per_pass` on this machine."""
     small = CpuSample(workloads, args, 0.25)
@@ -680,7 +680,7 @@ def host_threads():
 def cpu_baseline(workloads, args):
     from oracle import oracle
     threads = host_threads() if oracle.have("ref") else 1
-    sample = cpu_sample_for_budget(workloads, args, threads, 10.0)
+    sample = cpu_sample_for_seconds(workloads, args, threads, 10.0)
     gbs, full_s, detail, kind = sample.run(threads)
     return {"value": round(gbs, 4), "unit": "GB/s", "cores": threads, "kind": kind,
             "sample": "per configuration a leading slab of the batch (sizes in detail), time scaled linearly to the full batch",
@@ -698,7 +698,7 @@ def run_reference(args):
     threads = host_threads() if oracle.have("ref") else 1
     # every pass is a bounded sample; the whole run stays within a few minutes
     per_pass = max(0.5, min(8.0, 150.0 / (args.steps + args.warmup)))
-    sample = cpu_sample_for_budget(workloads, args, threads, per_pass)
+    sample = cpu_sample_for_seconds(workloads, args, threads, per_pass)
     for _ in range(args.warmup):
         sample.run(threads)
     vals, secs = [], []

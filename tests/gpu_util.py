@@ -41,7 +41,7 @@ def run_case_on_gpu(case, transient=False, tensors=None):
 def oracle_case(case, kind="port", tensors=None, absolute=False):
     tensors = tensors or cases.make_tensors(case)
     names = sorted(tensors)
-    # absolute=True gives sum|terms| per output entry, the scale rounding differences are judged on
+    # absolute=True gives sum|terms| per output entry, the scale rounding differences are measured against
     work = {n: (np.abs(tensors[n]) if absolute else tensors[n].copy()) for n in names}
     oracle.run(kind, [work[n] for n in names], cases.as_oracle_program(case, names), multi=case[3])
     return work
