@@ -409,18 +409,51 @@ bool plan_invariant_gemm(DimensionedKernel &k, int ki, Step &s)
 bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
 {
     const Names out = k.OutputVar.IndexNames;
-    if (out.size() != 3 || !distinct(out) || k.ContractionIndexNames.size() != 1 || k.GetNumInputVars() != 2) return false;
-    const std::string e = out[0], i = out[1], j = out[2], kk = k.ContractionIndexNames[0];
+    if ((out.size() != 3 && out.size() != 2) || !distinct(out) || k.ContractionIndexNames.size() != 1 || k.GetNumInputVars() != 2) return false;
+    const std::string e = out[0], kk = k.ContractionIndexNames[0];
     int av = -1, bv = -1;
-    for (int vari = 0; vari < 2; ++vari)
+    std::int64_t m = 1, n = 1;
+    if (out.size() == 3)
     {
-        const Names idx = indices_of(k, vari);
-        if (idx == Names{e, i, kk} && av < 0) av = vari;
-        else if (idx == Names{e, kk, j} && bv < 0) bv = vari;
-        else return false;
+        const std::string i = out[1], j = out[2];
+        for (int vari = 0; vari < 2; ++vari)
+        {
+            const Names idx = indices_of(k, vari);
+            if (idx == Names{e, i, kk} && av < 0) av = vari;
+            else if (idx == Names{e, kk, j} && bv < 0) bv = vari;
+            else return false;
+        }
+        m = extent_of(k, i);
+        n = extent_of(k, j);
+    }
+    else
+    {
+        // element matrix times element vector, Y_e_i = M_e_i_k X_e_k (n = 1), or vector times matrix, Y_e_j = X_e_k M_e_k_j (m = 1)
+        const std::string x = out[1];
+        for (int vari = 0; vari < 2; ++vari)
+        {
+            const Names idx = indices_of(k, vari);
+            if (idx == Names{e, kk}) continue;
+            if (idx == Names{e, x, kk} && av < 0) av = vari;
+            else if (idx == Names{e, kk, x} && bv < 0) bv = vari;
+            else return false;
+        }
+        if ((av < 0) == (bv < 0)) return false;          // exactly one of the two is the matrix
+        const int vec = av >= 0 ? 1 - av : 1 - bv;
+        if (indices_of(k, vec) != Names{e, kk}) return false;
+        if (av >= 0)
+        {
+            bv = vec;
+            m = extent_of(k, x);
+        }
+        else
+        {
+            av = vec;
+            n = extent_of(k, x);
+        }
     }
     if (av < 0 || bv < 0) return false;
-    const std::int64_t batch = extent_of(k, e), m = extent_of(k, i), n = extent_of(k, j), kn = extent_of(k, kk);
+    const std::int64_t batch = extent_of(k, e), kn = extent_of(k, kk);
     if (!acro_b200_batched_gemm_supported(static_cast<int>(m), static_cast<int>(n), static_cast<int>(kn))) return false;
     s = Step();
     s.family = Family::BatchedGemm;
@@ -440,7 +473,8 @@ bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
     s.flops = 2 * batch * m * n * kn;
     std::ostringstream note;
     note << batch << " products of " << m << "x" << kn << " by " << kn << "x" << n;
-    if (m <= 16 && n <= 16 && kn <= 16) note << ", streaming tiles of matrices through shared memory (bulk copies), 4x1 strips per thread, no fused multiply-add";
+    if (m == 1 || n == 1) note << ", matrix-vector: streaming tiles of elements through shared memory (bulk copies), rows rotated across banks";
+    else if (m <= 16 && n <= 16 && kn <= 16) note << ", streaming tiles of matrices through shared memory (bulk copies), 4x1 strips per thread, no fused multiply-add";
     else
     {
         note << ", persistent CTAs, 3-stage asynchronous bulk-copy ring, fp64 tensor cores (mma.sync m8n8k4)";

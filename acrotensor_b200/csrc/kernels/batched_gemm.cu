@@ -373,6 +373,9 @@ int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t 
     if (A == nullptr || B == nullptr || C == nullptr) return fail_invalid("acro_b200_batched_gemm: null argument");
     if (batch < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_batched_gemm: bad batch or operator");
     if (!acro_b200_batched_gemm_supported(m, n, k)) return fail_unsupported("acro_b200_batched_gemm: m, n, k must be in 1..64");
+    // one column or one row: a matrix-vector product per element
+    if (n == 1 && batched_matvec_supported(m, k)) return batched_matvec_launch(A, B, C, batch, m, k, 0, op, as_stream(stream));
+    if (m == 1 && batched_matvec_supported(k, n)) return batched_matvec_launch(B, A, C, batch, k, n, 1, op, as_stream(stream));
     if (batched_gemm_small_supported(m, n, k)) return batched_gemm_small_launch(A, B, C, batch, m, n, k, op, as_stream(stream));
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_batched_gemm");

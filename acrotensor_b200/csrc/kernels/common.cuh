@@ -37,6 +37,10 @@ inline int launch_status(const char *where)
 bool batched_gemm_small_supported(int m, int n, int k);
 int batched_gemm_small_launch(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int op, cudaStream_t stream);
 
+// Element matrix times element vector (batched_matvec.cu): form 0  Y_i = sum_k M_ik X_k, form 1  Y_j = sum_k X_k M_kj.
+bool batched_matvec_supported(int rows, int cols);
+int batched_matvec_launch(const double *M, const double *X, double *Y, int64_t batch, int rows, int cols, int form, int op, cudaStream_t stream);
+
 __host__ __device__ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }

