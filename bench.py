@@ -611,6 +611,20 @@ def run_ops(args):
         per_op[key] = e
         del dev, t, operands
 
+    # element matrices: products of small matrices, and their action on element vectors
+    for key, kernel, shapes_of, full in [
+            ("batched_gemm_8", "C_e_i_j = A_e_i_k B_e_k_j", lambda n: [(n, 8, 8), (n, 8, 8), (n, 8, 8)], 1 << 21),
+            ("batched_gemm_27", "C_e_i_j = A_e_i_k B_e_k_j", lambda n: [(n, 27, 27), (n, 27, 27), (n, 27, 27)], 1 << 17),
+            ("batched_matvec_27", "Y_e_i = M_e_i_j X_e_j", lambda n: [(n, 27), (n, 27, 27), (n, 27)], 1 << 18),
+            ("batched_matvec_64", "Y_e_i = M_e_i_j X_e_j", lambda n: [(n, 64), (n, 64, 64), (n, 64)], 1 << 15)]:
+        n = max(64, int(full * args.scale))
+        dev = [dev_tensor(shape, -1, 1) for shape in shapes_of(n)]
+        operands = [bind(t) for t in dev]
+        plan_line = [l for l in te.GetImplementation(kernel, *operands).splitlines() if l.startswith("step 0")][0]
+        per_op[key] = entry(timed(lambda: te(kernel, *operands)), float(plan_line.split("bytes=")[1].split()[0]),
+                            "%d elements; %s" % (n, plan_line.split("|")[1].strip()[:90]))
+        del dev, operands
+
     ms, nbytes = headline
     print(json.dumps({"metric": "batch_inv_det_throughput", "value": round(nbytes / ms * 1e-6, 1), "unit": "GB/s", "n_gpus": 1,
                       "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "dtype": "f64",

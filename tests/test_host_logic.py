@@ -257,3 +257,19 @@ def test_entry_points_validate_their_arguments_before_touching_a_device():
     assert lib().acro_b200_rank1_gemm(p, p, p, p, 8, 65, 4, 4, 0, None) == _lib.EUNSUPPORTED
     assert lib().acro_b200_sumfact_mass(p, p, p, p, 8, 6, 7, None) == _lib.EUNSUPPORTED
     assert lib().acro_b200_halo_exchange_sum(None, p, None) == _lib.EINVAL
+
+
+def test_element_matrix_vector_strings_are_planned_as_batched_products():
+    te = ab.TensorEngine("Cuda")
+
+    def plan(kernel, *shapes):
+        t = [ab.Tensor(s, hdata=np.zeros(s)) for s in shapes]
+        return [l for l in te.GetImplementation(kernel, *t).splitlines() if l.startswith("step 0")][0]
+
+    assert "family=batched_gemm" in plan("Y_e_i = M_e_i_j X_e_j", (100, 27), (100, 27, 27), (100, 27)) and "27x27 by 27x1" in \
+        plan("Y_e_i = M_e_i_j X_e_j", (100, 27), (100, 27, 27), (100, 27))
+    assert "1x5 by 5x9" in plan("Y_e_j = X_e_k M_e_k_j", (100, 9), (100, 5), (100, 5, 9))
+    assert "family=batched_gemm" in plan("Y_e_i = X_e_j M_e_i_j", (100, 27), (100, 27), (100, 27, 27))      # operands the other way round
+    assert "family=generic" in plan("Y_e_i = M_e_i_j X_j", (100, 27), (100, 27, 27), (27,))                # a shared vector is another shape
+    assert "family=generic" in plan("Y_e_i = A_e_k B_e_k", (100, 27), (100, 27), (100, 27))
+    assert "family=generic" in plan("Y_e_i = M_e_i_j X_e_j", (100, 70), (100, 70, 70), (100, 70))          # beyond 64
