@@ -94,3 +94,36 @@ def test_other_families_stay_inside_their_buffers():
     oracle.contract("port", "D_e_m_n_k1_k2_k3 = Det_e_k1_k2_k3 X_e_k1_k2_k3_n_j X_e_k1_k2_k3_m_j", ref, det, x, x)
     assert np.array_equal(d, ref)
     assert lib().acro_b200_device_status() == 0
+
+
+@pytest.mark.parametrize("kernel,shapes", [
+    # batched products: streaming variant (ragged last tile), zero-padded tensor-core variant, matrix-vector forms
+    ("C_e_i_j = A_e_i_k B_e_k_j", [(1001, 5, 7), (1001, 5, 3), (1001, 3, 7)]),
+    ("C_e_i_j += A_e_i_k B_e_k_j", [(203, 27, 27), (203, 27, 27), (203, 27, 27)]),
+    ("C_e_i_j = A_e_i_k B_e_k_j", [(77, 33, 50), (77, 33, 64), (77, 64, 50)]),
+    ("Y_e_i = M_e_i_j X_e_j", [(1003, 27), (1003, 27, 27), (1003, 27)]),
+    ("Y_e_j = X_e_k M_e_k_j", [(501, 9), (501, 5), (501, 5, 9)]),
+    # assembly strings through the GEMM (odd sizes: ragged tiles in every direction), the register-blocked generic kernel
+    ("M_e_i_j = W_e_q B_q_i C_q_j", [(705, 9, 7), (705, 125), (125, 9), (125, 7)]),
+    ("M_e_i1_i2_j1_j2=B_k1_i1 B_k1_j1 B_k2_i2 B_k2_j2 D_e_k1_k2", [(4100, 4, 4, 4, 4), (4, 4), (4, 4), (4, 4), (4, 4), (4100, 4, 4)]),
+    ("T_e_i1_i2_k3 = B_k3_i3 U_e_i1_i2_i3", [(5003, 4, 4, 5), (5, 4), (5003, 4, 4, 4)]),
+])
+def test_matrix_families_stay_inside_their_buffers(kernel, shapes):
+    import torch
+    rng = np.random.default_rng(len(kernel))
+    host = [rng.random(s) * 2 - 1 for s in shapes]
+    start = host[0].copy()
+    g = [Guarded(torch, h) for h in host]
+    te = ab.TensorEngine("Cuda")
+    te(kernel, g[0].tensor, *[x.tensor for x in g[1:]])
+    torch.cuda.synchronize()
+    for x in g:
+        assert x.intact(), kernel
+    assert lib().acro_b200_device_status() == 0
+    g[0].tensor.MoveFromGPU()
+    plain = kernel.replace("+=", "=")
+    prod, mags = np.zeros_like(start), np.zeros_like(start)
+    oracle.contract("port", plain, prod, *host[1:])
+    oracle.contract("port", plain, mags, *[np.abs(h) for h in host[1:]])
+    ref = start + prod if "+=" in kernel else prod
+    assert oracle.parity_error(host[0], ref, mags + (np.abs(start) if "+=" in kernel else 0)) <= 1e-12
