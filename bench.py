@@ -541,19 +541,21 @@ def run_ops(args):
     headline = (ms, nbytes)
     del J, inv, det, TJ, TI, TD
 
-    # scatter / sum-gather on a 3D trilinear-like numbering: 8 entries per element, neighbours share entries
+    # scatter / sum-gather on a 3D triquadratic-like numbering: 27 entries per element on a (2n+1)^3 grid of
+    # domain entries, faces / edges / corners shared by neighbouring elements
     n = max(2, int(round(E ** (1.0 / 3.0))))
+    side = 2 * n + 1
     ex, ey, ez = torch.meshgrid(torch.arange(n), torch.arange(n), torch.arange(n), indexing="ij")
-    corner = (ex * (n + 1) + ey) * (n + 1) + ez
-    offs = torch.tensor([(a * (n + 1) + b) * (n + 1) + c for a in (0, 1) for b in (0, 1) for c in (0, 1)])
+    corner = ((2 * ex) * side + 2 * ey) * side + 2 * ez
+    offs = torch.tensor([(a * side + b) * side + c for a in (0, 1, 2) for b in (0, 1, 2) for c in (0, 1, 2)])
     mapping = (corner.reshape(-1, 1) + offs.reshape(1, -1)).to(torch.int32).reshape(-1).numpy()
-    domain, rng_size = (n + 1) ** 3, mapping.size
+    domain, rng_size = side ** 3, mapping.size
     M = ab.IndexMapping(domain, rng_size, mapping)
     M.ComputeInverse()
     x, u = dev_tensor((domain,)), torch.empty((rng_size,), device="cuda", dtype=torch.float64)
     TX, TU = bind(x), bind(u)
     per_op["flat_indexed_scatter"] = entry(timed(lambda: te.FlatIndexedScatter(TU, TX, M)), rng_size * 12 + domain * 8,
-                                           "%d elements x 8 entries from %d domain entries; bytes = map + output + domain once" % (n ** 3, domain))
+                                           "%d elements x 27 entries from %d domain entries; bytes = map + output + domain once" % (n ** 3, domain))
     per_op["flat_indexed_sum_gather"] = entry(timed(lambda: te.FlatIndexedSumGather(TX, TU, M)), rng_size * 12 + domain * 12,
                                               "same mapping; bytes = input + inverse map + offsets + output")
     del x, u, TX, TU, M
