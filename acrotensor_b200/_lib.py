@@ -66,6 +66,8 @@ SIGNATURES = {
     "acro_b200_scale": (_I, [_P, _I64, _D, _P]),
     "acro_b200_generic_launch": (_I, [ctypes.POINTER(GenericDesc), _P, ctypes.POINTER(_P), _P, _SZ, _P]),
     "acro_b200_generic_scratch_bytes": (_SZ, [ctypes.POINTER(GenericDesc)]),
+    "acro_b200_permute_supported": (_I, [ctypes.POINTER(GenericDesc)]),
+    "acro_b200_permute": (_I, [ctypes.POINTER(GenericDesc), _P, _P, _P]),
     "acro_b200_generic_blocking": (_I, [ctypes.POINTER(GenericDesc), ctypes.POINTER(ctypes.c_int)]),
     "acro_b200_generic_uses_wide_kernel": (_I, [ctypes.POINTER(GenericDesc)]),
     "acro_b200_reduce_batch_scratch_bytes": (_SZ, [_I]),

@@ -171,6 +171,11 @@ void B200Executor::Run(std::vector<Tensor *> &outputs, std::vector<std::vector<T
                           "gemm");
                 break;
             }
+            case plan::Family::Permute:
+            {
+                check_abi(acro_b200_permute(&s.generic, out->GetDeviceData(), ins[0]->GetDeviceData(), stream), "permute");
+                break;
+            }
             default:
                 ACROBATIC_ASSERT(false, "Planned a kernel family that is not built into this library.");
         }

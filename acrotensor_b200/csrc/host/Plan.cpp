@@ -594,6 +594,34 @@ bool plan_sumfact_mass(DimensionedMultiKernel &mk, Step &s)
     return true;
 }
 
+// ---------------------------------------------------------------- permute
+// Out = In with the indices in another order, fastest index included: a tiled transpose.
+bool plan_permute(DimensionedKernel &k, int ki, Step &s)
+{
+    if (k.GetNumInputVars() != 1 || !k.ContractionIndexNames.empty()) return false;
+    const Names out = k.OutputVar.IndexNames, in = indices_of(k, 0);
+    if (out.size() != in.size() || !distinct(out) || !distinct(in)) return false;
+    Step g = plan_generic(k, ki);
+    if (!acro_b200_permute_supported(&g.generic)) return false;
+    // both fastest indices long enough to fill the 32 x 32 tiles, and enough data to matter
+    std::int64_t ext_fo = 0, ext_fi = 0, total = 1;
+    for (int l = 0; l < g.generic.n_loops; ++l)
+    {
+        total *= g.generic.extent[l];
+        if (g.generic.out_step[l] == 1 && g.generic.extent[l] > 1) ext_fo = g.generic.extent[l];
+        if (g.generic.in_step[0][l] == 1 && g.generic.extent[l] > 1) ext_fi = g.generic.extent[l];
+    }
+    if (ext_fo < 16 || ext_fi < 16 || total < (std::int64_t(1) << 16)) return false;
+    s = g;
+    s.family = Family::Permute;
+    s.zero_fill_first = false;
+    std::ostringstream note;
+    note << "tiled transpose: 32x32 tiles over the fastest output index (" << ext_fo << ") and the fastest input index (" << ext_fi
+         << "), " << total << " entries";
+    s.note = note.str();
+    return true;
+}
+
 Step plan_single(DimensionedKernel &k, int ki)
 {
     Step s;
@@ -604,6 +632,7 @@ Step plan_single(DimensionedKernel &k, int ki)
     if (plan_pointwise_sym(k, ki, s)) return s;
     if (plan_rank1_gemm(k, ki, s)) return s;
     if (plan_batched_gemm(k, ki, s)) return s;
+    if (plan_permute(k, ki, s)) return s;
     if (plan_invariant_gemm(k, ki, s)) return s;
     return plan_generic(k, ki);
 }
@@ -621,6 +650,7 @@ const char *FamilyName(Family f)
         case Family::BatchedGemm: return "batched_gemm";
         case Family::SumfactMass: return "sumfact_mass";
         case Family::InvariantGemm: return "invariant_gemm";
+        case Family::Permute: return "permute";
     }
     return "?";
 }

@@ -24,7 +24,8 @@ enum class Family
     Rank1Gemm,
     BatchedGemm,
     SumfactMass,
-    InvariantGemm
+    InvariantGemm,
+    Permute
 };
 
 const char *FamilyName(Family f);

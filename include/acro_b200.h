@@ -113,6 +113,16 @@ size_t acro_b200_generic_scratch_bytes(const acro_b200_generic_desc *desc);
 int acro_b200_generic_blocking(const acro_b200_generic_desc *desc, int *loop);
 
 /*
+ * permute: out (op)= the single input with its indices in another order ("A_i_j = B_j_i").  The descriptor is
+ * the generic one with no contracted loop (n_outer = n_loops, n_inputs = 1, every loop carried by both
+ * tensors).  Used when the fastest index of the input is not the fastest index of the output: 32 x 32 tiles
+ * over those two indices go through shared memory, so that loads and stores are both contiguous.  The
+ * reference's generator copies entry by entry (exec/CudaExecutor.cpp:520-604), strided on one side.
+ */
+int acro_b200_permute_supported(const acro_b200_generic_desc *desc);
+int acro_b200_permute(const acro_b200_generic_desc *desc, double *out, const double *in, void *stream);
+
+/*
  * reduce_batch:  out[f] (op)= sum_{n<rows} A[n*F + f] * (w ? w[n] : 1),  f < F.
  * The contracted batch index is the slowest dimension of A (README kernel
  * "S_i_j = A_n_i_j B_n").  Streams A once (8*F + 8 bytes per row), keeps

@@ -51,7 +51,7 @@ def families(plan):
     return [line.split("family=")[1].split()[0] for line in plan.splitlines() if "family=" in line]
 
 
-BIT_EXACT_FAMILIES = {"generic", "pointwise_sym"}
+BIT_EXACT_FAMILIES = {"generic", "pointwise_sym", "permute"}
 
 
 def dev_ptr(t):
