@@ -603,7 +603,7 @@ bool plan_permute(DimensionedKernel &k, int ki, Step &s)
     if (out.size() != in.size() || !distinct(out) || !distinct(in)) return false;
     Step g = plan_generic(k, ki);
     if (!acro_b200_permute_supported(&g.generic)) return false;
-    // both fastest indices long enough to fill the 32 x 32 tiles, and enough data to matter
+    // both fastest indices long enough to fill a good part of the 64 x 64 tiles, and enough data to matter
     std::int64_t ext_fo = 0, ext_fi = 0, total = 1;
     for (int l = 0; l < g.generic.n_loops; ++l)
     {
@@ -616,7 +616,7 @@ bool plan_permute(DimensionedKernel &k, int ki, Step &s)
     s.family = Family::Permute;
     s.zero_fill_first = false;
     std::ostringstream note;
-    note << "tiled transpose: 32x32 tiles over the fastest output index (" << ext_fo << ") and the fastest input index (" << ext_fi
+    note << "tiled transpose: 64x64 tiles over the fastest output index (" << ext_fo << ") and the fastest input index (" << ext_fi
          << "), " << total << " entries";
     s.note = note.str();
     return true;

@@ -1,8 +1,8 @@
 // permute: Out (op)= In with the indices in another order ("A_i_j = B_j_i", "Z_m_e_k = D_e_k_m").
 //
 // When the fastest index of the input is not the fastest index of the output, one side of a
-// thread-per-entry copy is strided.  Here 32 x 32 tiles over (fastest output index, fastest input
-// index) go through shared memory (rows padded to 33), so that both the loads and the stores of a
+// thread-per-entry copy is strided.  Here 64 x 64 tiles over (fastest output index, fastest input
+// index) go through shared memory (rows padded to 65), so that both the loads and the stores of a
 // warp are contiguous runs; the other indices are flattened into the grid.  Pure data movement:
 // bit-identical by construction.
 #include "common.cuh"
@@ -12,8 +12,9 @@ using namespace acro_b200_detail;
 namespace
 {
 
-constexpr int kTile = 32;
-constexpr int kRows = 8;        // block = 32 x 8 threads, four rows of a tile each
+constexpr int kTile = 64;
+constexpr int kLanes = 32;
+constexpr int kRows = 8;        // block = 32 x 8 threads; a thread moves 16 entries of a tile, all loads in flight before the barrier
 
 struct PermuteArgs
 {
@@ -27,7 +28,7 @@ struct PermuteArgs
     long long tiles_fo, tiles_fi;
 };
 
-__global__ void __launch_bounds__(kTile * kRows)
+__global__ void __launch_bounds__(kLanes * kRows)
 permute_kernel(const PermuteArgs a)
 {
     __shared__ double tile[kTile][kTile + 1];
@@ -52,22 +53,30 @@ permute_kernel(const PermuteArgs a)
 #pragma unroll
     for (int r = ty; r < kTile; r += kRows)
     {
-        const long long fo = fo0 + r, fi = fi0 + tx;
-        if (fo < a.ext_fo && fi < a.ext_fi) tile[r][tx] = a.in[base_in + fo * a.in_fo + fi];
+#pragma unroll
+        for (int c = tx; c < kTile; c += kLanes)
+        {
+            const long long fo = fo0 + r, fi = fi0 + c;
+            if (fo < a.ext_fo && fi < a.ext_fi) tile[r][c] = a.in[base_in + fo * a.in_fo + fi];
+        }
     }
     __syncthreads();
     // store: lanes along the output's fastest index
 #pragma unroll
     for (int r = ty; r < kTile; r += kRows)
     {
-        const long long fi = fi0 + r, fo = fo0 + tx;
-        if (fo < a.ext_fo && fi < a.ext_fi)
+#pragma unroll
+        for (int c = tx; c < kTile; c += kLanes)
         {
-            double *dst = a.out + base_out + fi * a.out_fi + fo;
-            const double v = tile[tx][r];
-            if (a.op == ACRO_B200_OP_ASSIGN) *dst = v;
-            else if (a.op == ACRO_B200_OP_ADD) *dst = __dadd_rn(*dst, v);
-            else *dst = __dsub_rn(*dst, v);
+            const long long fi = fi0 + r, fo = fo0 + c;
+            if (fo < a.ext_fo && fi < a.ext_fi)
+            {
+                double *dst = a.out + base_out + fi * a.out_fi + fo;
+                const double v = tile[c][r];
+                if (a.op == ACRO_B200_OP_ASSIGN) *dst = v;
+                else if (a.op == ACRO_B200_OP_ADD) *dst = __dadd_rn(*dst, v);
+                else *dst = __dsub_rn(*dst, v);
+            }
         }
     }
 }
@@ -124,7 +133,7 @@ int acro_b200_permute(const acro_b200_generic_desc *d, double *out, const double
     a.tiles_fi = (a.ext_fi + kTile - 1) / kTile;
     const long long blocks = slices * a.tiles_fo * a.tiles_fi;
     if (blocks > 0x7fffffffLL) return fail_unsupported("acro_b200_permute: more than 2^31 tiles");
-    permute_kernel<<<static_cast<unsigned int>(blocks), dim3(kTile, kRows), 0, as_stream(stream)>>>(a);
+    permute_kernel<<<static_cast<unsigned int>(blocks), dim3(kLanes, kRows), 0, as_stream(stream)>>>(a);
     return launch_status("acro_b200_permute");
 }
 

@@ -115,7 +115,7 @@ int acro_b200_generic_blocking(const acro_b200_generic_desc *desc, int *loop);
 /*
  * permute: out (op)= the single input with its indices in another order ("A_i_j = B_j_i").  The descriptor is
  * the generic one with no contracted loop (n_outer = n_loops, n_inputs = 1, every loop carried by both
- * tensors).  Used when the fastest index of the input is not the fastest index of the output: 32 x 32 tiles
+ * tensors).  Used when the fastest index of the input is not the fastest index of the output: 64 x 64 tiles
  * over those two indices go through shared memory, so that loads and stores are both contiguous.  The
  * reference's generator copies entry by entry (exec/CudaExecutor.cpp:520-604), strided on one side.
  */
