@@ -393,6 +393,42 @@ void launch_blocked(const BlockedArgs &a, int entries, double *out, const InputP
     }
 }
 
+// Same layout on both sides and nothing contracted ("A_i = B_i", "A_i_j += B_i_j"): a flat stream,
+// two entries per access where both pointers are 16-byte aligned.
+__global__ void __launch_bounds__(256)
+generic_flat_kernel(double *__restrict__ out, const double *__restrict__ in, int64_t n, int op, int vec2)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (vec2)
+    {
+        double2 *o2 = reinterpret_cast<double2 *>(out);
+        const double2 *i2 = reinterpret_cast<const double2 *>(in);
+        for (int64_t p = first; p < n / 2; p += stride)
+        {
+            double2 v = __ldcs(i2 + p);
+            if (op != ACRO_B200_OP_ASSIGN)
+            {
+                const double2 old = o2[p];
+                v.x = op == ACRO_B200_OP_ADD ? __dadd_rn(old.x, v.x) : __dsub_rn(old.x, v.x);
+                v.y = op == ACRO_B200_OP_ADD ? __dadd_rn(old.y, v.y) : __dsub_rn(old.y, v.y);
+            }
+            __stcs(o2 + p, v);
+        }
+        if (first == 0 && (n & 1))
+        {
+            const double v = in[n - 1];
+            out[n - 1] = op == ACRO_B200_OP_ASSIGN ? v : (op == ACRO_B200_OP_ADD ? __dadd_rn(out[n - 1], v) : __dsub_rn(out[n - 1], v));
+        }
+        return;
+    }
+    for (int64_t p = first; p < n; p += stride)
+    {
+        const double v = __ldcs(in + p);
+        out[p] = op == ACRO_B200_OP_ASSIGN ? v : (op == ACRO_B200_OP_ADD ? __dadd_rn(out[p], v) : __dsub_rn(out[p], v));
+    }
+}
+
 // Few output entries but a long contraction (for example "S_a = X_n_a Y_n_a"): the terms of
 // every output entry are cut into `chunks` contiguous ranges, one CTA per (entry, range); the
 // threads of a CTA take interleaved terms (coalesced for a unit-stride innermost index) and
@@ -601,6 +637,27 @@ extern "C" int acro_b200_generic_launch(const acro_b200_generic_desc *desc, doub
             default: generic_wide_kernel<0><<<grid, kWideThreads, 0, s>>>(*desc, out, ins, terms, ws); break;
         }
         return launch_status("acro_b200_generic_launch (wide)");
+    }
+    if (desc->n_inputs == 1 && desc->n_loops == desc->n_outer)
+    {
+        // one input, nothing contracted, the same step in both tensors for every loop: a flat stream
+        bool flat = true;
+        for (int l = 0; l < desc->n_loops; ++l) flat = flat && (desc->extent[l] == 1 || desc->in_step[0][l] == desc->out_step[l]);
+        int64_t expect = 1;
+        for (int l = desc->n_loops - 1; l >= 0 && flat; --l)
+        {
+            if (desc->extent[l] == 1) continue;
+            flat = desc->out_step[l] == expect;          // dense, in loop order
+            expect *= desc->extent[l];
+        }
+        if (flat)
+        {
+            const int vec2 = (aligned16(out) && aligned16(ins.p[0])) ? 1 : 0;
+            const int64_t work = vec2 ? (outer_points + 1) / 2 : outer_points;
+            const int64_t need = (work + 255) / 256, most = static_cast<int64_t>(sm_count()) * 16;
+            generic_flat_kernel<<<static_cast<int>(need < most ? need : most), 256, 0, s>>>(out, ins.p[0], outer_points, desc->op, vec2);
+            return launch_status("acro_b200_generic_launch (flat)");
+        }
     }
     const BlockedPlan bp = blocked_plan(*desc);
     if (bp.entries > 1)

@@ -74,3 +74,25 @@ def test_blocked_and_plain_variants_agree_bitwise():
     got_s, plan_s = gu.run_case_on_gpu(small, tensors=ts)
     assert "thread per output entry" in plan_s and "output entries along" in plan_l
     assert np.array_equal(got_s["A"], got_l["A"][:64, :32])
+
+
+@pytest.mark.parametrize("kernel,shape,offset", [("A_i = B_i", (100001,), 0), ("A_i_j += B_i_j", (333, 301), 0), ("A_i_j_k -= B_i_j_k", (50, 7, 11), 0),
+                                                 ("A_i = B_i", (4099,), 1), ("A_i_j += B_i_j", (64, 65), 1)])
+def test_same_layout_streams(kernel, shape, offset):
+    """One input, nothing contracted, the same layout on both sides: the flat streaming path (pairs of entries
+    when both device pointers are 16-byte aligned, single entries otherwise)."""
+    import torch
+    import acrotensor_b200 as ab
+    rng = np.random.default_rng(int(np.prod(shape)))
+    a0, b = rng.random(shape), rng.random(shape)
+    host_a = a0.copy()
+    n = a0.size
+    bufs = [torch.zeros(n + offset, dtype=torch.float64, device="cuda") for _ in range(2)]
+    bufs[0][offset:] = torch.from_numpy(a0.reshape(-1)).cuda()
+    bufs[1][offset:] = torch.from_numpy(b.reshape(-1)).cuda()
+    A = ab.Tensor(shape, hdata=host_a, ddata=bufs[0].data_ptr() + 8 * offset, ongpu=True)
+    B = ab.Tensor(shape, hdata=b, ddata=bufs[1].data_ptr() + 8 * offset, ongpu=True)
+    ab.TensorEngine("Cuda")(kernel, A, B)
+    A.MoveFromGPU()
+    expect = b if "+=" not in kernel and "-=" not in kernel else (a0 + b if "+=" in kernel else a0 - b)
+    assert np.array_equal(host_a, expect)
