@@ -475,10 +475,11 @@ bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
     note << batch << " products of " << m << "x" << kn << " by " << kn << "x" << n;
     if (m == 1 || n == 1) note << ", matrix-vector: streaming tiles of elements through shared memory (bulk copies), rows rotated across banks";
     else if (m <= 16 && n <= 16 && kn <= 16) note << ", streaming tiles of matrices through shared memory (bulk copies), 4x1 strips per thread, no fused multiply-add";
+    else if ((m > 32 || n > 32 || kn > 32) && !(m == 64 && n == 64 && kn == 64)) note << ", 64x64 tiles of every product through the tensor-core GEMM (mma.sync m8n8k4)";
     else
     {
         note << ", persistent CTAs, 3-stage asynchronous bulk-copy ring, fp64 tensor cores (mma.sync m8n8k4)";
-        if (!(m == n && n == kn && (m == 32 || m == 64))) note << ", zero-padded on chip to " << (std::max(m, std::max(n, kn)) <= 32 ? 32 : 64);
+        if (!(m == n && n == kn && (m == 32 || m == 64))) note << ", zero-padded on chip to 32";
     }
     s.note = note.str();
     return true;

@@ -48,6 +48,7 @@ struct GemmArgs
     const double *P;
     double *C;
     int64_t M, N, K, lda, ldp, ldc;
+    int64_t batch, stride_a, stride_p, stride_c;      // independent products: element e starts stride_* doubles further on
     int op;
     int wide_a, wide_p;       // 16-byte copies allowed for the operand
     int shift_a;              // lda is odd: rows of A that start on an odd element sit one column to the right in shared memory
@@ -75,8 +76,10 @@ __device__ __forceinline__ void copy8(double *dst, const double *src, int bytes)
 
 // Copies slab `kt` of tile (tm, tn) into slot `stage`; k4 = slab depth padded to a multiple of four.
 template <int KT>
-__device__ __forceinline__ void issue_slab(Smem<KT> &s, const GemmArgs &a, int64_t tm, int64_t tn, int64_t kt, int k4, int stage)
+__device__ __forceinline__ void issue_slab(Smem<KT> &s, const GemmArgs &a, int64_t e, int64_t tm, int64_t tn, int64_t kt, int k4, int stage)
 {
+    const double *A = a.A + e * a.stride_a, *P = a.P + e * a.stride_p;
+    const int par_e = static_cast<int>((e & a.stride_a) & 1);      // parity of the element's first entry (the base of a.A is 16-byte aligned)
     constexpr int LDA = Smem<KT>::LDA;
     constexpr int CPR = KT / 2;                 // 16-byte chunks per row of the A tile
     const int tid = threadIdx.x;
@@ -88,7 +91,7 @@ __device__ __forceinline__ void issue_slab(Smem<KT> &s, const GemmArgs &a, int64
     if (a.wide_a && !a.shift_a && a.wide_p && rows == T && cols == T && depth == KT)
     {
         // interior slab: whole 16-byte chunks only, addresses by shifts
-        const double *ga = a.A + row0 * a.lda + k0, *gp = a.P + k0 * a.ldp + col0;
+        const double *ga = A + row0 * a.lda + k0, *gp = P + k0 * a.ldp + col0;
 #pragma unroll
         for (int i = 0; i < T * CPR / NT; ++i)
         {
@@ -120,10 +123,10 @@ __device__ __forceinline__ void issue_slab(Smem<KT> &s, const GemmArgs &a, int64
         {
             const int c = tid + i * NT;
             const int r = c / CPR, cc = c % CPR;
-            const int sh = a.shift_a ? static_cast<int>((row0 + r) & 1) : 0;
+            const int sh = a.shift_a ? (par_e ^ static_cast<int>((row0 + r) & a.lda & 1)) : 0;
             if (r < rows && 2 * cc < k4 + sh)
             {
-                const double *src = a.A + (row0 + r) * a.lda + k0;
+                const double *src = A + (row0 + r) * a.lda + k0;
                 const int c0 = 2 * cc - sh;           // slab column of the chunk's first slot
                 double *dst = &s.A[stage][r * LDA + 2 * cc];
                 const int left = depth - c0;          // valid doubles from this chunk on
@@ -131,11 +134,11 @@ __device__ __forceinline__ void issue_slab(Smem<KT> &s, const GemmArgs &a, int64
                 else copy16(dst, left > 0 ? src + c0 : a.A, left >= 2 ? 16 : (left == 1 ? 8 : 0));
             }
         }
-        if (a.shift_a && k4 == KT && tid < rows && ((row0 + tid) & 1))
+        if (a.shift_a && k4 == KT && tid < rows && (par_e ^ static_cast<int>((row0 + tid) & a.lda & 1)))
         {
             // the extra chunk of a shifted row: slab column KT - 1 and one slot of padding
             const int left = depth - (KT - 1);
-            copy16(&s.A[stage][tid * LDA + KT], left > 0 ? a.A + (row0 + tid) * a.lda + k0 + KT - 1 : a.A, left > 0 ? 8 : 0);
+            copy16(&s.A[stage][tid * LDA + KT], left > 0 ? A + (row0 + tid) * a.lda + k0 + KT - 1 : a.A, left > 0 ? 8 : 0);
         }
     }
     else
@@ -145,7 +148,7 @@ __device__ __forceinline__ void issue_slab(Smem<KT> &s, const GemmArgs &a, int64
         {
             const int c = tid + i * NT;
             const int r = c / KT, col = c % KT;
-            if (r < rows && col < k4) copy8(&s.A[stage][r * LDA + col], a.A + (row0 + r) * a.lda + k0 + (col < depth ? col : 0), col < depth ? 8 : 0);
+            if (r < rows && col < k4) copy8(&s.A[stage][r * LDA + col], A + (row0 + r) * a.lda + k0 + (col < depth ? col : 0), col < depth ? 8 : 0);
         }
     }
     // P tile: k4 x cols; rows of the padding are written as zeros
@@ -159,7 +162,7 @@ __device__ __forceinline__ void issue_slab(Smem<KT> &s, const GemmArgs &a, int64
             if (r < k4 && 2 * cc < cols)
             {
                 const int left = r < depth ? cols - 2 * cc : 0;
-                copy16(&s.P[stage][r * LD + 2 * cc], left > 0 ? a.P + (k0 + r) * a.ldp + col0 + 2 * cc : a.P, left >= 2 ? 16 : (left == 1 ? 8 : 0));
+                copy16(&s.P[stage][r * LD + 2 * cc], left > 0 ? P + (k0 + r) * a.ldp + col0 + 2 * cc : a.P, left >= 2 ? 16 : (left == 1 ? 8 : 0));
             }
         }
     }
@@ -170,7 +173,7 @@ __device__ __forceinline__ void issue_slab(Smem<KT> &s, const GemmArgs &a, int64
         {
             const int c = tid + i * NT;
             const int r = c >> 6, col = c & 63;
-            if (r < k4 && col < cols) copy8(&s.P[stage][r * LD + col], r < depth ? a.P + (k0 + r) * a.ldp + col0 + col : a.P, r < depth ? 8 : 0);
+            if (r < k4 && col < cols) copy8(&s.P[stage][r * LD + col], r < depth ? P + (k0 + r) * a.ldp + col0 + col : a.P, r < depth ? 8 : 0);
         }
     }
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&s.full[stage])) : "memory");
@@ -188,7 +191,7 @@ gemm_f64_kernel(const GemmArgs a)
     const int g = lane >> 2, t = lane & 3;
     const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 32;
     constexpr int MT = 2, NTL = 4;
-    const bool pairs = aligned16(a.C) && a.ldc % 2 == 0;      // entry pairs of C sit on 16-byte boundaries
+    const bool pairs = aligned16(a.C) && a.ldc % 2 == 0 && a.stride_c % 2 == 0;      // entry pairs of C sit on 16-byte boundaries
 
     if (tid == 0)
     {
@@ -205,26 +208,29 @@ gemm_f64_kernel(const GemmArgs a)
     // more than the step's tensor-core loop
     const int tiles_m = static_cast<int>((a.M + T - 1) / T), tiles_n = static_cast<int>((a.N + T - 1) / T);
     const int slabs = static_cast<int>((a.K + KT - 1) / KT);
-    const int n_tiles = tiles_m * tiles_n;
+    const int per_matrix = tiles_m * tiles_n;
+    const int n_tiles = per_matrix * static_cast<int>(a.batch);
     const int last_k4 = (static_cast<int>(a.K - static_cast<int64_t>(slabs - 1) * KT) + 3) & ~3;
 
     // position of the slab being multiplied and of the slab being fetched (one step ahead); tiles run
     // down the rows of C first, so that CTAs working side by side share the same slabs of P
-    int tile = blockIdx.x, kt = 0, tm = tile % tiles_m, tn = tile / tiles_m;
-    int f_tile = tile, f_kt = 0, f_tm = tm, f_tn = tn;
+    // tile number -> (element, column tile, row tile), row tile fastest
+    int tile = blockIdx.x, kt = 0, te = tile / per_matrix, tm = (tile % per_matrix) % tiles_m, tn = (tile % per_matrix) / tiles_m;
+    int f_tile = tile, f_kt = 0, f_te = te, f_tm = tm, f_tn = tn;
     unsigned int fetched = 0;      // slabs fetched so far: slab number `fetched` goes to slot fetched % STAGES
 
     auto fetch = [&]() {
         const unsigned int slot = fetched % STAGES, use = fetched / STAGES;      // use: how often the slot was filled before
         if (use > 0 && !mbar_wait(&s.empty[slot], (use - 1) & 1u)) atomicExch(a.wait_flag, 1);
-        issue_slab<KT>(s, a, f_tm, f_tn, f_kt, f_kt == slabs - 1 ? last_k4 : KT, static_cast<int>(slot));
+        issue_slab<KT>(s, a, f_te, f_tm, f_tn, f_kt, f_kt == slabs - 1 ? last_k4 : KT, static_cast<int>(slot));
         ++fetched;
         if (++f_kt == slabs)
         {
             f_kt = 0;
             f_tile += gridDim.x;
-            f_tm = f_tile % tiles_m;
-            f_tn = f_tile / tiles_m;
+            f_te = f_tile / per_matrix;
+            f_tm = (f_tile % per_matrix) % tiles_m;
+            f_tn = (f_tile % per_matrix) / tiles_m;
         }
     };
 
@@ -247,7 +253,7 @@ gemm_f64_kernel(const GemmArgs a)
         const double *sp = s.P[stage];
         const int k4 = kt == slabs - 1 ? last_k4 : KT;
         // rows of A stored one column to the right (odd lda): m0 + mt * 8 is even, so the parity is that of tile row g
-        const int sh = a.shift_a ? ((tm * T + g) & 1) : 0;
+        const int sh = a.shift_a ? (static_cast<int>((te & a.stride_a) & 1) ^ static_cast<int>(g & a.lda & 1)) : 0;
 #pragma unroll 4
         for (int k0 = 0; k0 < k4; k0 += 4)
         {
@@ -275,7 +281,7 @@ gemm_f64_kernel(const GemmArgs a)
                 for (int nt = 0; nt < NTL; ++nt)
                 {
                     const int64_t j = col0 + n0 + nt * 8 + 2 * t;
-                    double *dst = a.C + i * a.ldc + j;
+                    double *dst = a.C + te * a.stride_c + i * a.ldc + j;
                     if (pairs && j + 1 < a.N)
                     {
                         // both entries of the lane as one 16-byte store: a quad writes a 64-byte row segment
@@ -301,19 +307,21 @@ gemm_f64_kernel(const GemmArgs a)
         {
             kt = 0;
             tile += gridDim.x;
-            tm = tile % tiles_m;
-            tn = tile / tiles_m;
+            te = tile / per_matrix;
+            tm = (tile % per_matrix) % tiles_m;
+            tn = (tile % per_matrix) / tiles_m;
         }
     }
 }
 
 }
 
-extern "C" int acro_b200_gemm(const double *A, const double *P, double *C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldp,
-                              int64_t ldc, int op, void *stream)
+extern "C" int acro_b200_gemm_batched(const double *A, const double *P, double *C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                      int64_t ldp, int64_t ldc, int64_t stride_a, int64_t stride_p, int64_t stride_c, int op, void *stream)
 {
     if (A == nullptr || P == nullptr || C == nullptr) return fail_invalid("acro_b200_gemm: null argument");
-    if (M < 1 || N < 1 || K < 1 || lda < K || ldp < N || ldc < N || op < 0 || op > 2) return fail_invalid("acro_b200_gemm: bad sizes, leading dimensions or operator");
+    if (batch < 1 || M < 1 || N < 1 || K < 1 || lda < K || ldp < N || ldc < N || op < 0 || op > 2 || stride_a < 0 || stride_p < 0 || stride_c < 0)
+        return fail_invalid("acro_b200_gemm: bad sizes, leading dimensions, strides or operator");
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_gemm");
     GemmArgs args;
@@ -326,15 +334,18 @@ extern "C" int acro_b200_gemm(const double *A, const double *P, double *C, int64
     args.lda = lda;
     args.ldp = ldp;
     args.ldc = ldc;
+    args.batch = batch;
+    args.stride_a = stride_a;
+    args.stride_p = stride_p;
+    args.stride_c = stride_c;
     args.op = op;
     args.wide_a = aligned16(A) ? 1 : 0;
-    args.shift_a = (args.wide_a && lda % 2 != 0) ? 1 : 0;
-    args.wide_p = (aligned16(P) && ldp % 2 == 0) ? 1 : 0;
+    args.shift_a = (args.wide_a && (lda % 2 != 0 || stride_a % 2 != 0)) ? 1 : 0;
+    args.wide_p = (aligned16(P) && ldp % 2 == 0 && stride_p % 2 == 0) ? 1 : 0;
     args.wait_flag = wait_flag_device_ptr();
     if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_gemm (status flag)");
-    const int64_t tiles = ((M + T - 1) / T) * ((N + T - 1) / T);
+    const int64_t tiles = batch * ((M + T - 1) / T) * ((N + T - 1) / T);
     if (tiles > (int64_t(1) << 30) || K > (int64_t(1) << 30)) return fail_unsupported("acro_b200_gemm: more than 2^30 tiles of C or K above 2^30");
-    // slab depth: the smallest that holds K in one slab, 64 beyond; CTAs per SM follow from the ring's size
     auto launch = [&](auto kernel, size_t smem, int per_sm) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (status != cudaSuccess) return fail_cuda(status, "acro_b200_gemm (shared memory opt-in)");
@@ -343,11 +354,17 @@ extern "C" int acro_b200_gemm(const double *A, const double *P, double *C, int64
         kernel<<<static_cast<int>(grid), NT, smem, as_stream(stream)>>>(args);
         return ACRO_B200_OK;
     };
-    int status;
     // Slab depth 32 with two CTAs per SM beats depth 64 with one for every K measured (K = 60 ... 1125: 24.7-30.4
     // against 16.0-30.0 TFLOP/s): one CTA's copies and stores overlap the other's tensor-core loop.
+    int status;
     if (K <= 16) status = launch(gemm_f64_kernel<16>, sizeof(Smem<16>), 3);
     else status = launch(gemm_f64_kernel<32>, sizeof(Smem<32>), 2);
     if (status != ACRO_B200_OK) return status;
     return launch_status("acro_b200_gemm");
+}
+
+extern "C" int acro_b200_gemm(const double *A, const double *P, double *C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldp,
+                              int64_t ldc, int op, void *stream)
+{
+    return acro_b200_gemm_batched(A, P, C, 1, M, N, K, lda, ldp, ldc, 0, 0, 0, op, stream);
 }

@@ -233,7 +233,7 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
 
 /*
  * batched_gemm:  C[e,i,j] (op)= sum_{k} A[e,i,k] * B[e,k,j]  for a batch of dense row-major
- * matrices ("C_e_i_j = A_e_i_k B_e_k_j"), any m, n, k in 1..64.  64^3 and 32^3: persistent CTAs,
+ * matrices ("C_e_i_j = A_e_i_k B_e_k_j"), any m, n, k (above 64: acro_b200_gemm_batched).  64^3 and 32^3: persistent CTAs,
  * three-stage asynchronous copy ring for A_e and B_e, fp64 tensor cores; other sizes above 16 use
  * the same kernel with the matrices zero-padded on chip to 32 or 64.  Every m, n, k <= 16 is
  * HBM-bound: tiles of matrices streamed through shared memory by bulk copies, separate multiply
@@ -258,6 +258,10 @@ int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t 
  */
 int acro_b200_gemm(const double *A, const double *P, double *C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldp,
                    int64_t ldc, int op, void *stream);
+/* `batch` independent products of that kind in one launch: element e uses A + e*stride_a, P + e*stride_p and
+ * C + e*stride_c (strides in doubles; 0 shares the operand between the elements). */
+int acro_b200_gemm_batched(const double *A, const double *P, double *C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda,
+                           int64_t ldp, int64_t ldc, int64_t stride_a, int64_t stride_p, int64_t stride_c, int op, void *stream);
 
 /*
  * sumfact_mass: the six-stage sum-factorised 3D mass operator as ONE kernel,

@@ -76,7 +76,7 @@ def test_batched_gemm_kernel(torch, batch, op, offset, n):
     ka, pa = to_dev(torch, a, offset)
     kb, pb = to_dev(torch, b)
     kc, pc = to_dev(torch, c0)
-    assert lib().acro_b200_batched_gemm_supported(n, n, n) == 1 and lib().acro_b200_batched_gemm_supported(n, n, 65) == 0
+    assert lib().acro_b200_batched_gemm_supported(n, n, n) == 1 and lib().acro_b200_batched_gemm_supported(n, n, 4097) == 0
     check(lib().acro_b200_batched_gemm(pa, pb, pc, batch, n, n, n, op, None))
     status_ok()
     got = kc.cpu().numpy().reshape(c0.shape)
@@ -127,7 +127,9 @@ def test_small_batched_gemm_kernel_is_bit_identical(torch, batch, m, n, k, op, o
 
 @pytest.mark.parametrize("batch,m,n,k,op,offset", [
     (1, 27, 27, 27, 0, 0), (500, 27, 27, 27, 0, 0), (301, 27, 27, 27, 1, 1), (64, 20, 33, 17, 0, 0), (40, 64, 64, 48, 2, 0), (90, 17, 64, 5, 0, 0),
-    (75, 33, 1, 64, 0, 1), (130, 48, 48, 48, 1, 0), (55, 18, 24, 30, 0, 0), (33, 32, 32, 31, 0, 0), (20, 63, 63, 63, 0, 1)])
+    (75, 33, 1, 64, 0, 1), (130, 48, 48, 48, 1, 0), (55, 18, 24, 30, 0, 0), (33, 32, 32, 31, 0, 0), (20, 63, 63, 63, 0, 1),
+    # above 64: tiles of every product through the GEMM kernel (odd sizes: shifted rows, 8-byte copies, ragged tiles)
+    (7, 125, 125, 125, 0, 0), (5, 125, 125, 125, 1, 1), (3, 65, 200, 33, 2, 0), (4, 128, 64, 96, 0, 0), (9, 100, 3, 129, 0, 0)])
 def test_padded_batched_gemm_kernel(torch, batch, m, n, k, op, offset):
     """Sizes between 17 and 64 that do not fill the 32- or 64-wide slots: zero-padded on chip, fp64 tensor cores."""
     rng = np.random.default_rng(batch + m + k)

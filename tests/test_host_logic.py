@@ -252,7 +252,7 @@ def test_entry_points_validate_their_arguments_before_touching_a_device():
     assert lib().acro_b200_gemm(p, p, p, 4, 4, 4, 3, 4, 4, 0, None) == _lib.EINVAL          # lda < K
     assert lib().acro_b200_gemm(p, p, p, 4, 4, 4, 4, 4, 4, 3, None) == _lib.EINVAL          # unknown operator
     assert b"acro_b200_gemm" in lib().acro_b200_last_error()
-    assert lib().acro_b200_batched_gemm(p, p, p, 1, 65, 4, 4, 0, None) == _lib.EUNSUPPORTED
+    assert lib().acro_b200_batched_gemm(p, p, p, 1, 4097, 4, 4, 0, None) == _lib.EUNSUPPORTED
     assert lib().acro_b200_batched_gemm(p, p, p, 0, 4, 4, 4, 0, None) == _lib.EINVAL
     assert lib().acro_b200_rank1_gemm(p, p, p, p, 8, 65, 4, 4, 0, None) == _lib.EUNSUPPORTED
     assert lib().acro_b200_sumfact_mass(p, p, p, p, 8, 6, 7, None) == _lib.EUNSUPPORTED
@@ -272,4 +272,4 @@ def test_element_matrix_vector_strings_are_planned_as_batched_products():
     assert "family=batched_gemm" in plan("Y_e_i = X_e_j M_e_i_j", (100, 27), (100, 27), (100, 27, 27))      # operands the other way round
     assert "family=generic" in plan("Y_e_i = M_e_i_j X_j", (100, 27), (100, 27, 27), (27,))                # a shared vector is another shape
     assert "family=generic" in plan("Y_e_i = A_e_k B_e_k", (100, 27), (100, 27), (100, 27))
-    assert "family=generic" in plan("Y_e_i = M_e_i_j X_e_j", (100, 70), (100, 70, 70), (100, 70))          # beyond 64
+    assert "family=generic" in plan("Y_e_i = M_e_i_j X_e_j", (100, 70), (100, 70, 70), (100, 70))          # matrix-vector beyond 64
