@@ -273,3 +273,25 @@ def test_element_matrix_vector_strings_are_planned_as_batched_products():
     assert "family=generic" in plan("Y_e_i = M_e_i_j X_j", (100, 27), (100, 27, 27), (27,))                # a shared vector is another shape
     assert "family=generic" in plan("Y_e_i = A_e_k B_e_k", (100, 27), (100, 27), (100, 27))
     assert "family=generic" in plan("Y_e_i = M_e_i_j X_e_j", (100, 70), (100, 70, 70), (100, 70))          # matrix-vector beyond 64
+
+
+def test_planner_routes_sizes_and_layouts_to_the_expected_variants():
+    te = ab.TensorEngine("Cuda")
+
+    def step0(kernel, *shapes):
+        t = [ab.Tensor(s, hdata=np.zeros(s)) for s in shapes]
+        return [l for l in te.GetImplementation(kernel, *t).splitlines() if l.startswith("step 0")][0]
+
+    gemm = "C_e_i_j = A_e_i_k B_e_k_j"
+    assert "streaming tiles of matrices" in step0(gemm, (10, 5, 7), (10, 5, 3), (10, 3, 7))
+    assert "zero-padded on chip to 32" in step0(gemm, (10, 27, 27), (10, 27, 27), (10, 27, 27))
+    assert "3-stage asynchronous bulk-copy ring" in step0(gemm, (10, 64, 64), (10, 64, 64), (10, 64, 64))
+    assert "64x64 tiles of every product" in step0(gemm, (10, 48, 48), (10, 48, 48), (10, 48, 48))
+    assert "64x64 tiles of every product" in step0(gemm, (4, 125, 100), (4, 125, 90), (4, 90, 100))
+    # index reorderings: a tiled transpose only when the fastest index changes and both runs are long enough
+    assert "family=permute" in step0("A_i_j=B_j_i", (300, 400), (400, 300))
+    assert "family=permute" in step0("A_e_i_j = B_e_j_i", (3000, 27, 27), (3000, 27, 27))
+    assert "family=generic" in step0("A_i_j_k = B_j_i_k", (100, 90, 64), (90, 100, 64))
+    assert "family=generic" in step0("A_i_j=B_j_i", (4, 5), (5, 4))
+    # a plain matrix product is an assembly string with the batch index i and a single invariant factor
+    assert "family=invariant_gemm" in step0("C_i_j = A_i_k B_k_j", (512, 512), (512, 512), (512, 512))
