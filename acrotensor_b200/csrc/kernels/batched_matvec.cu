@@ -12,6 +12,7 @@
 // that the rows of a warp (a multiple of 128 bytes apart when cols is even) fall into different
 // banks.  The order of the sum therefore differs from the reference's and fused multiply-add is
 // used: results agree within the usual 1e-12 * sum|terms|.  Form 1 walks k in order, lanes along j.
+// Measured on B200: 8 x 8 100 %, 16 x 16 101 %, 27 x 27 98 %, 40 x 40 97 %, 64 x 64 98 % of measured HBM bandwidth.
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -21,7 +22,7 @@ namespace
 {
 
 constexpr int kThreads = 256;
-constexpr int kStageBudget = 48 * 1024;      // bytes of one stage
+constexpr int kStageBudget = 32 * 1024;      // bytes of one stage
 
 struct MatvecArgs
 {
@@ -167,16 +168,17 @@ int batched_matvec_launch(const double *M, const double *X, double *Y, int64_t b
     args.cols = cols;
     args.form = form;
     args.op = op;
-    const int xin = form == 0 ? cols : rows, yout = form == 0 ? rows : cols;
+    const int xin = form == 0 ? cols : rows;
     const int per_elem_bytes = (rows * cols + xin) * 8;
     int group = kStageBudget / per_elem_bytes;
     if (group > 256) group = 256;
     if (group > 1) group &= ~1;                       // even: the spans of a tile stay 16-byte multiples
     if (group < 1) group = 1;
     args.group = group;
-    // lanes per result entry: enough that a tile keeps the CTA busy; they must share a warp
-    int split = 1;
-    while (form == 0 && split < 8 && group * yout * split < 2 * kThreads && 2 * split <= cols) split *= 2;      // form 1 keeps one lane per entry: lanes along j
+    // lanes per result entry (form 0; form 1 keeps one lane per entry, lanes along j).  Measured on B200 with 32 KB
+    // stages: rows of 8 and 16 entries run at the HBM rate with one lane per row (two lanes: 71 % and 91 %), rows of
+    // 27, 40 and 64 entries with two (one lane: 86 %, 72 %, 69 %; four lanes: 75 %, 74 %, 89 %).
+    const int split = (form == 0 && cols >= 24) ? 2 : 1;
     args.split = split;
     args.bulk_in = (aligned16(M) && aligned16(X) && (static_cast<long long>(group) * rows * cols) % 2 == 0 &&
                     (static_cast<long long>(group) * xin) % 2 == 0) ? 1 : 0;
@@ -186,7 +188,7 @@ int batched_matvec_launch(const double *M, const double *X, double *Y, int64_t b
     cudaError_t status = cudaFuncSetAttribute(batched_matvec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (status != cudaSuccess) return fail_cuda(status, "acro_b200_batched_gemm (shared memory opt-in)");
     int per_sm = static_cast<int>((200 * 1024) / (smem + 1024));
-    if (per_sm > 4) per_sm = 4;
+    if (per_sm > 8) per_sm = 8;
     if (per_sm < 1) per_sm = 1;
     const int64_t tiles = (batch + group - 1) / group;
     int64_t grid = static_cast<int64_t>(sms) * per_sm;
