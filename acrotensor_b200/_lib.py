@@ -62,6 +62,7 @@ SIGNATURES = {
     "acro_b200_last_error": (_S, []),
     "acro_b200_device_count": (_I, []),
     "acro_b200_device_status": (_I, []),
+    "acro_b200_set_context": (_I, [_P]),
     "acro_b200_fill": (_I, [_P, _I64, _D, _P]),
     "acro_b200_scale": (_I, [_P, _I64, _D, _P]),
     "acro_b200_generic_launch": (_I, [ctypes.POINTER(GenericDesc), _P, ctypes.POINTER(_P), _P, _SZ, _P]),

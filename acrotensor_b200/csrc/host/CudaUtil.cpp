@@ -1,8 +1,8 @@
 // Device discovery, context/stream selection and the CUDA error convention.
 #include "CudaUtil.hpp"
+#include "acro_b200.h"
 
 #include <cuda_runtime_api.h>
-#include <dlfcn.h>
 #include <iostream>
 
 namespace acro
@@ -29,19 +29,7 @@ bool isCudaReady()
 
 void setCudaContext(void *cuda_context)
 {
-    // The driver library is looked up at run time so that this library still loads on a
-    // machine without a driver (where only the host-side planner can be used).
-    typedef int (*set_current_fn)(void *);
-    static set_current_fn set_current = nullptr;
-    if (set_current == nullptr)
-    {
-        void *driver = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
-        ACROBATIC_ASSERT(driver != nullptr, "setCudaContext: the CUDA driver library is not available.");
-        set_current = reinterpret_cast<set_current_fn>(dlsym(driver, "cuCtxSetCurrent"));
-        ACROBATIC_ASSERT(set_current != nullptr, "setCudaContext: cuCtxSetCurrent not found in the CUDA driver library.");
-    }
-    int status = set_current(cuda_context);
-    ACROBATIC_ASSERT(status == 0, "setCudaContext failed with driver status " + std::to_string(status));
+    if (acro_b200_set_context(cuda_context) != ACRO_B200_OK) throw_error(std::string("setCudaContext: ") + acro_b200_last_error());
 }
 
 void setCudaStream(void *cuda_stream) { g_stream = cuda_stream; }

@@ -2,7 +2,9 @@
 #include "common.cuh"
 #include "tma.cuh"
 
+#include <dlfcn.h>
 #include <mutex>
+#include <string>
 #include <vector>
 
 namespace acro_b200_detail
@@ -51,13 +53,21 @@ int sm_count()
 
 static __device__ int g_wait_timed_out = 0;
 
+namespace
+{
+// Address of g_wait_timed_out on each device.  A device symbol has one address per CUDA context, so
+// acro_b200_set_context clears the table.
+constexpr int kMaxDevices = 64;
+std::mutex g_wait_flag_lock;
+int *g_wait_flag_of_device[kMaxDevices] = {nullptr};
+}
+
 namespace acro_b200_detail
 {
 int *wait_flag_device_ptr()
 {
-    constexpr int kMaxDevices = 64;
-    static std::mutex lock;
-    static int *ptr_of_device[kMaxDevices] = {nullptr};
+    std::mutex &lock = g_wait_flag_lock;
+    int **ptr_of_device = g_wait_flag_of_device;
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
     std::lock_guard<std::mutex> guard(lock);
@@ -110,6 +120,30 @@ int acro_b200_device_count(void)
         return 0;
     }
     return n;
+}
+
+int acro_b200_set_context(void *cuda_context)
+{
+    // The driver library is looked up at run time so that this library still loads on a
+    // machine without a driver (where only the host-side planner can be used).
+    typedef int (*set_current_fn)(void *);
+    static set_current_fn set_current = nullptr;
+    if (set_current == nullptr)
+    {
+        void *driver = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+        if (driver == nullptr) return fail_cuda(cudaErrorNoDevice, "acro_b200_set_context (the CUDA driver library is not available)");
+        set_current = reinterpret_cast<set_current_fn>(dlsym(driver, "cuCtxSetCurrent"));
+        if (set_current == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_set_context (cuCtxSetCurrent not found in the driver library)");
+    }
+    const int status = set_current(cuda_context);
+    if (status != 0)
+    {
+        set_last_error("acro_b200_set_context: cuCtxSetCurrent failed with driver status " + std::to_string(status));
+        return ACRO_B200_ECUDA;
+    }
+    std::lock_guard<std::mutex> guard(g_wait_flag_lock);
+    for (int d = 0; d < kMaxDevices; ++d) g_wait_flag_of_device[d] = nullptr;
+    return ACRO_B200_OK;
 }
 
 int acro_b200_device_status(void)

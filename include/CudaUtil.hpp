@@ -8,6 +8,14 @@
 #include <string>
 #include "Error.hpp"
 
+// User code built with -DACRO_HAVE_CUDA gets the driver and runtime declarations through this
+// header, as it does from util/CudaUtil.hpp:17-21 (it may call cudaMalloc or cuCtxCreate itself).
+// Without the macro no CUDA header is needed to use the library.
+#ifdef ACRO_HAVE_CUDA
+#include <cuda.h>
+#include <cuda_runtime.h>
+#endif
+
 namespace acro
 {
 

@@ -61,6 +61,13 @@ int acro_b200_device_count(void);
  * acroCudaErrorCheck after a launch (util/CudaUtil.hpp:59-89). */
 int acro_b200_device_status(void);
 
+/* Makes an externally created driver context (a CUcontext passed as void*) current for the
+ * calling thread, as acro::setCudaContext does (util/CudaUtil.hpp:93-98); later calls of this
+ * thread run in it.  Device addresses the library looked up in the previous context are
+ * forgotten.  Device memory, tensors and engines created in one context must not be used in
+ * another. */
+int acro_b200_set_context(void *cuda_context);
+
 /* ---------------------------------------------------------------- kernel layer */
 
 /* Aout[i] = val / Aout[i] *= c.  Replace CudaSet / CudaMult, util/CudaUtil.cpp:123-140. */

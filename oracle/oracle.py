@@ -24,11 +24,15 @@ _libs = {}
 
 
 def build(verbose=False):
-    """Compile the C restatement, and the reference-backed checker when the
-    reference checkout is present (otherwise the prebuilt one is used)."""
+    """Compile the C restatement and, when the reference checkout is present, the
+    reference-backed checker and the reference's unit tests linked against the product
+    library (otherwise the prebuilt ones are used).  The product library is built first."""
     targets = ["oracle"]
     if os.path.isdir(os.path.join(REFERENCE_CHECKOUT, "exec")):
         targets.append("ref")
+    product = os.path.join(HERE, "..", "acrotensor_b200", "libacrotensor.so")
+    if os.path.isdir(os.path.join(REFERENCE_CHECKOUT, "unittest")) and os.path.exists(product):
+        targets.append("ref_tests")
     cmd = ["make", "-C", HERE, "REF=" + REFERENCE_CHECKOUT] + targets
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode:
