@@ -149,8 +149,8 @@ void B200Executor::Run(std::vector<Tensor *> &outputs, std::vector<std::vector<T
             }
             case plan::Family::BatchedGemm:
             {
-                check_abi(acro_b200_batched_gemm(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), out->GetDeviceData(), s.rows,
-                                                 s.sizes[0], s.sizes[1], s.sizes[2], s.op, stream),
+                check_abi(acro_b200_batched_gemm_t(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), out->GetDeviceData(), s.rows,
+                                                   s.sizes[0], s.sizes[1], s.sizes[2], s.sizes[3], s.sizes[4], s.op, stream),
                           "batched_gemm");
                 break;
             }

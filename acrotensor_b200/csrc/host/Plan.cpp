@@ -411,16 +411,19 @@ bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
     const Names out = k.OutputVar.IndexNames;
     if ((out.size() != 3 && out.size() != 2) || !distinct(out) || k.ContractionIndexNames.size() != 1 || k.GetNumInputVars() != 2) return false;
     const std::string e = out[0], kk = k.ContractionIndexNames[0];
-    int av = -1, bv = -1;
+    int av = -1, bv = -1, ta = 0, tb = 0;
     std::int64_t m = 1, n = 1;
     if (out.size() == 3)
     {
+        // the input that carries i is A (stored i x k, or k x i: transposed), the one that carries j is B (k x j, or j x k)
         const std::string i = out[1], j = out[2];
         for (int vari = 0; vari < 2; ++vari)
         {
             const Names idx = indices_of(k, vari);
             if (idx == Names{e, i, kk} && av < 0) av = vari;
+            else if (idx == Names{e, kk, i} && av < 0) { av = vari; ta = 1; }
             else if (idx == Names{e, kk, j} && bv < 0) bv = vari;
+            else if (idx == Names{e, j, kk} && bv < 0) { bv = vari; tb = 1; }
             else return false;
         }
         m = extent_of(k, i);
@@ -454,7 +457,9 @@ bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
     }
     if (av < 0 || bv < 0) return false;
     const std::int64_t batch = extent_of(k, e), kn = extent_of(k, kk);
-    if (!acro_b200_batched_gemm_supported(static_cast<int>(m), static_cast<int>(n), static_cast<int>(kn))) return false;
+    if (m == 1) ta = 0;      // a row or a column is stored the same way in both orders
+    if (n == 1) tb = 0;
+    if (!acro_b200_batched_gemm_t_supported(static_cast<int>(m), static_cast<int>(n), static_cast<int>(kn), ta, tb)) return false;
     s = Step();
     s.family = Family::BatchedGemm;
     s.kernels = {ki};
@@ -464,6 +469,8 @@ bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
     s.sizes[0] = static_cast<int>(m);
     s.sizes[1] = static_cast<int>(n);
     s.sizes[2] = static_cast<int>(kn);
+    s.sizes[3] = ta;
+    s.sizes[4] = tb;
     TensorRef a, b;
     a.ki = b.ki = ki;
     a.vari = av;
@@ -473,13 +480,15 @@ bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
     s.flops = 2 * batch * m * n * kn;
     std::ostringstream note;
     note << batch << " products of " << m << "x" << kn << " by " << kn << "x" << n;
+    if (ta) note << " (first operand stored transposed)";
+    if (tb) note << " (second operand stored transposed)";
     if (m == 1 || n == 1) note << ", matrix-vector: streaming tiles of elements through shared memory (bulk copies), rows rotated across banks";
     else if (m <= 16 && n <= 16 && kn <= 16) note << ", streaming tiles of matrices through shared memory (bulk copies), 4x1 strips per thread, no fused multiply-add";
-    else if ((m > 32 || n > 32 || kn > 32) && !(m == 64 && n == 64 && kn == 64)) note << ", 64x64 tiles of every product through the tensor-core GEMM (mma.sync m8n8k4)";
+    else if (!ta && !tb && (m > 32 || n > 32 || kn > 32) && !(m == 64 && n == 64 && kn == 64)) note << ", 64x64 tiles of every product through the tensor-core GEMM (mma.sync m8n8k4)";
     else
     {
         note << ", persistent CTAs, 3-stage asynchronous bulk-copy ring, fp64 tensor cores (mma.sync m8n8k4)";
-        if (!(m == n && n == kn && (m == 32 || m == 64))) note << ", zero-padded on chip to 32";
+        if (!(m == n && n == kn && (m == 32 || m == 64))) note << ", zero-padded on chip to " << ((m > 32 || n > 32 || kn > 32) ? 64 : 32);
     }
     s.note = note.str();
     return true;

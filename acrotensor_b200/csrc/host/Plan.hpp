@@ -53,7 +53,7 @@ struct Step
     acro_b200_generic_desc generic;
     acro_b200_pointwise_desc pointwise;
     std::int64_t rows = 0;           // reduce_batch / batch count of the GEMM families
-    int sizes[4] = {0, 0, 0, 0};     // family-specific compile-time sizes
+    int sizes[5] = {0, 0, 0, 0, 0};  // family-specific sizes and flags
     std::vector<TensorRef> elided;   // transient outputs this step keeps on chip
 };
 

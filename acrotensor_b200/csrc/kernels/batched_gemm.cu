@@ -16,6 +16,10 @@
 // Measured alternatives on B200 (E = 2^14): one bulk copy (TMA) per matrix row issued by a
 // single warp 0.597 ms, the same copies spread over all warps 0.351 ms, cp.async 0.339 ms.
 //
+// Transposed operands (A_e stored as k x m, B_e stored as n x k; template flags TA, TB): the copies
+// are the same, only the fragment loads swap their two strides; with rows padded to 4 (mod 16)
+// doubles both orientations are free of bank conflicts.
+//
 // Algorithmic HBM traffic: 3 * 8 * 64 * 64 = 98,304 bytes per element; 2 * 64^3 = 524,288
 // flops per element (arithmetic intensity 5.33 flop/byte, the fp64 ridge of a B200).
 #include "common.cuh"
@@ -77,7 +81,13 @@ __device__ __forceinline__ void issue_element_load(Smem<N> &s, const GemmArgs &a
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&s.full[stage])) : "memory");
 }
 
-template <int N>
+// Fragments of mma.sync m8n8k4 from a padded slot: A(i, kk) and B(kk, j) in either storage order.
+template <int LD, bool T>
+__device__ __forceinline__ double frag_a(const double *sa, int i, int kk) { return T ? sa[kk * LD + i] : sa[i * LD + kk]; }
+template <int LD, bool T>
+__device__ __forceinline__ double frag_b(const double *sb, int kk, int j) { return T ? sb[j * LD + kk] : sb[kk * LD + j]; }
+
+template <int N, bool TA, bool TB>
 __global__ void __launch_bounds__(NT, N == 64 ? 1 : 4)
 batched_gemm_kernel(const GemmArgs a)
 {
@@ -147,9 +157,9 @@ batched_gemm_kernel(const GemmArgs a)
         {
             double af[MT], bf[NTL];
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) af[mt] = sa[(m0 + mt * 8 + g) * LD + k0 + t];
+            for (int mt = 0; mt < MT; ++mt) af[mt] = frag_a<LD, TA>(sa, m0 + mt * 8 + g, k0 + t);
 #pragma unroll
-            for (int nt = 0; nt < NTL; ++nt) bf[nt] = sb[(k0 + t) * LD + n0 + nt * 8 + g];
+            for (int nt = 0; nt < NTL; ++nt) bf[nt] = frag_b<LD, TB>(sb, k0 + t, n0 + nt * 8 + g);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -188,6 +198,7 @@ struct PaddedArgs
     double *C;
     int64_t batch;
     int m, n, k, op;
+    int rows_a, cols_a, rows_b, cols_b;      // the operands as stored: A is m x k (k x m when transposed), B is k x n (n x k)
     int *wait_flag;
     int wide;        // rows of A and B are 16-byte multiples on 16-byte boundaries: 16-byte copies
 };
@@ -200,10 +211,10 @@ __device__ __forceinline__ void issue_padded_load(Smem<N> &s, const PaddedArgs &
     const double *ga = a.A + e * a.m * a.k, *gb = a.B + e * a.k * a.n;
     if (a.wide)
     {
-        const int ca = a.k / 2, cb = a.n / 2;          // 16-byte chunks per row
+        const int ca = a.cols_a / 2, cb = a.cols_b / 2;          // 16-byte chunks per row
         int col = tid % ca, row = tid / ca;
         const int sc = NT % ca, sr = NT / ca;
-        for (int c = tid; row < a.m; c += NT)
+        for (int c = tid; row < a.rows_a; c += NT)
         {
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&s.A[stage][row * LD + col * 2])), "l"(ga + c * 2) : "memory");
             col += sc;
@@ -212,7 +223,7 @@ __device__ __forceinline__ void issue_padded_load(Smem<N> &s, const PaddedArgs &
         }
         col = tid % cb, row = tid / cb;
         const int tc = NT % cb, tr = NT / cb;
-        for (int c = tid; row < a.k; c += NT)
+        for (int c = tid; row < a.rows_b; c += NT)
         {
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&s.B[stage][row * LD + col * 2])), "l"(gb + c * 2) : "memory");
             col += tc;
@@ -222,29 +233,29 @@ __device__ __forceinline__ void issue_padded_load(Smem<N> &s, const PaddedArgs &
     }
     else
     {
-        int col = tid % a.k, row = tid / a.k;
-        const int sc = NT % a.k, sr = NT / a.k;
-        for (int c = tid; row < a.m; c += NT)
+        int col = tid % a.cols_a, row = tid / a.cols_a;
+        const int sc = NT % a.cols_a, sr = NT / a.cols_a;
+        for (int c = tid; row < a.rows_a; c += NT)
         {
             asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_addr(&s.A[stage][row * LD + col])), "l"(ga + c) : "memory");
             col += sc;
-            if (col >= a.k) { col -= a.k; ++row; }
+            if (col >= a.cols_a) { col -= a.cols_a; ++row; }
             row += sr;
         }
-        col = tid % a.n, row = tid / a.n;
-        const int tc = NT % a.n, tr = NT / a.n;
-        for (int c = tid; row < a.k; c += NT)
+        col = tid % a.cols_b, row = tid / a.cols_b;
+        const int tc = NT % a.cols_b, tr = NT / a.cols_b;
+        for (int c = tid; row < a.rows_b; c += NT)
         {
             asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_addr(&s.B[stage][row * LD + col])), "l"(gb + c) : "memory");
             col += tc;
-            if (col >= a.n) { col -= a.n; ++row; }
+            if (col >= a.cols_b) { col -= a.cols_b; ++row; }
             row += tr;
         }
     }
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&s.full[stage])) : "memory");
 }
 
-template <int N>
+template <int N, bool TA, bool TB>
 __global__ void __launch_bounds__(NT, N == 64 ? 1 : 4)
 batched_gemm_padded_kernel(const PaddedArgs a)
 {
@@ -311,9 +322,9 @@ batched_gemm_padded_kernel(const PaddedArgs a)
             {
                 double af[MT], bf[NTL];
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) af[mt] = sa[(m0 + mt * 8 + g) * LD + k0 + t];
+                for (int mt = 0; mt < MT; ++mt) af[mt] = frag_a<LD, TA>(sa, m0 + mt * 8 + g, k0 + t);
 #pragma unroll
-                for (int nt = 0; nt < NTL; ++nt) bf[nt] = sb[(k0 + t) * LD + n0 + nt * 8 + g];
+                for (int nt = 0; nt < NTL; ++nt) bf[nt] = frag_b<LD, TB>(sb, k0 + t, n0 + nt * 8 + g);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -348,45 +359,74 @@ batched_gemm_padded_kernel(const PaddedArgs a)
 }
 
 template <int N>
-int launch_padded(const PaddedArgs &args, int sms, cudaStream_t stream)
+int launch_padded(const PaddedArgs &args, int trans_a, int trans_b, int sms, cudaStream_t stream)
 {
     const size_t smem = sizeof(Smem<N>);
-    cudaError_t status = cudaFuncSetAttribute(batched_gemm_padded_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    auto kernel = trans_a ? (trans_b ? batched_gemm_padded_kernel<N, true, true> : batched_gemm_padded_kernel<N, true, false>)
+                          : (trans_b ? batched_gemm_padded_kernel<N, false, true> : batched_gemm_padded_kernel<N, false, false>);
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (status != cudaSuccess) return fail_cuda(status, "acro_b200_batched_gemm (shared memory opt-in)");
     int64_t grid = static_cast<int64_t>(sms) * (N == 64 ? 1 : 4);
     if (grid > args.batch) grid = args.batch;
-    batched_gemm_padded_kernel<N><<<static_cast<int>(grid), NT, smem, stream>>>(args);
+    kernel<<<static_cast<int>(grid), NT, smem, stream>>>(args);
     return launch_status("acro_b200_batched_gemm (padded)");
+}
+
+template <int N>
+int launch_ring(const GemmArgs &args, int trans_a, int trans_b, int sms, cudaStream_t stream)
+{
+    const size_t smem = sizeof(Smem<N>);
+    auto kernel = trans_a ? (trans_b ? batched_gemm_kernel<N, true, true> : batched_gemm_kernel<N, true, false>)
+                          : (trans_b ? batched_gemm_kernel<N, false, true> : batched_gemm_kernel<N, false, false>);
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_batched_gemm (shared memory opt-in)");
+    int64_t grid = static_cast<int64_t>(sms) * (N == 64 ? 1 : 4);
+    if (grid > args.batch) grid = args.batch;
+    kernel<<<static_cast<int>(grid), NT, smem, stream>>>(args);
+    return launch_status("acro_b200_batched_gemm");
 }
 
 }
 
 extern "C" {
 
-int acro_b200_batched_gemm_supported(int m, int n, int k)
+int acro_b200_batched_gemm_t_supported(int m, int n, int k, int trans_a, int trans_b)
 {
     if (m < 1 || n < 1 || k < 1 || m > 4096 || n > 4096 || k > 4096) return 0;
     // a single row or column is a matrix-vector product: streamed for matrices up to 64 x 64, else left to the generic kernel
     if ((m == 1 || n == 1) && (m > 64 || n > 64 || k > 64)) return 0;
+    // transposed operands: the kernels that stage whole matrices in shared memory (up to 64 x 64)
+    if ((trans_a || trans_b) && (m > 64 || n > 64 || k > 64)) return 0;
     return 1;
 }
 
-int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int op, void *stream)
+int acro_b200_batched_gemm_supported(int m, int n, int k) { return acro_b200_batched_gemm_t_supported(m, n, k, 0, 0); }
+
+int acro_b200_batched_gemm_t(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int trans_a, int trans_b, int op,
+                             void *stream)
 {
     if (A == nullptr || B == nullptr || C == nullptr) return fail_invalid("acro_b200_batched_gemm: null argument");
     if (batch < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_batched_gemm: bad batch or operator");
-    if (!acro_b200_batched_gemm_supported(m, n, k)) return fail_unsupported("acro_b200_batched_gemm: m, n, k must be in 1..4096");
-    // one column or one row: a matrix-vector product per element
-    if (n == 1 && batched_matvec_supported(m, k)) return batched_matvec_launch(A, B, C, batch, m, k, 0, op, as_stream(stream));
-    if (m == 1 && batched_matvec_supported(k, n)) return batched_matvec_launch(B, A, C, batch, k, n, 1, op, as_stream(stream));
-    if ((m > 32 || n > 32 || k > 32) && !(m == 64 && n == 64 && k == 64))
+    trans_a = trans_a ? 1 : 0;
+    trans_b = trans_b ? 1 : 0;
+    if (m == 1) trans_a = 0;      // a row or a column is stored the same way in both orders
+    if (n == 1) trans_b = 0;
+    if (!acro_b200_batched_gemm_t_supported(m, n, k, trans_a, trans_b))
+        return fail_unsupported("acro_b200_batched_gemm: m, n, k must be in 1..4096 (1..64 with a transposed operand or a single row or column)");
+    // one column or one row: a matrix-vector product per element; a transposed matrix swaps the two forms
+    if (n == 1 && batched_matvec_supported(m, k))
+        return trans_a ? batched_matvec_launch(A, B, C, batch, k, m, 1, op, as_stream(stream)) : batched_matvec_launch(A, B, C, batch, m, k, 0, op, as_stream(stream));
+    if (m == 1 && batched_matvec_supported(k, n))
+        return trans_b ? batched_matvec_launch(B, A, C, batch, n, k, 0, op, as_stream(stream)) : batched_matvec_launch(B, A, C, batch, k, n, 1, op, as_stream(stream));
+    const bool plain = !trans_a && !trans_b;
+    if (plain && (m > 32 || n > 32 || k > 32) && !(m == 64 && n == 64 && k == 64))
     {
         // 64 x 64 tiles of every product through the tensor-core GEMM kernel (measured 11-12 % faster than zero-padding
         // 40^3 and 48^3 into the 64-wide slots of the ring below)
         return acro_b200_gemm_batched(A, B, C, batch, m, n, k, k, n, n, static_cast<int64_t>(m) * k, static_cast<int64_t>(k) * n,
                                       static_cast<int64_t>(m) * n, op, stream);
     }
-    if (batched_gemm_small_supported(m, n, k)) return batched_gemm_small_launch(A, B, C, batch, m, n, k, op, as_stream(stream));
+    if (batched_gemm_small_supported(m, n, k)) return batched_gemm_small_launch(A, B, C, batch, m, n, k, trans_a, trans_b, op, as_stream(stream));
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_batched_gemm");
 
@@ -411,18 +451,22 @@ int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t 
         pa.n = n;
         pa.k = k;
         pa.op = op;
+        pa.rows_a = trans_a ? k : m;
+        pa.cols_a = trans_a ? m : k;
+        pa.rows_b = trans_b ? n : k;
+        pa.cols_b = trans_b ? k : n;
         pa.wait_flag = args.wait_flag;
-        pa.wide = (aligned16(A) && aligned16(B) && k % 2 == 0 && n % 2 == 0 && (m * k) % 2 == 0 && (k * n) % 2 == 0) ? 1 : 0;
-        return launch_padded<32>(pa, sms, as_stream(stream));      // sizes 17..32; larger ones went to the GEMM kernel above
+        pa.wide = (aligned16(A) && aligned16(B) && pa.cols_a % 2 == 0 && pa.cols_b % 2 == 0 && (m * k) % 2 == 0 && (k * n) % 2 == 0) ? 1 : 0;
+        // sizes 17..32; plain products with a larger extent went to the GEMM kernel above, transposed ones use the 64-wide slots
+        if (m <= 32 && n <= 32 && k <= 32) return launch_padded<32>(pa, trans_a, trans_b, sms, as_stream(stream));
+        return launch_padded<64>(pa, trans_a, trans_b, sms, as_stream(stream));
     }
-    auto kernel = m == 64 ? batched_gemm_kernel<64> : batched_gemm_kernel<32>;
-    const size_t smem = m == 64 ? sizeof(Smem<64>) : sizeof(Smem<32>);
-    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_batched_gemm (shared memory opt-in)");
-    int64_t grid = static_cast<int64_t>(sms) * (m == 64 ? 1 : 4);
-    if (grid > batch) grid = batch;
-    kernel<<<static_cast<int>(grid), NT, smem, as_stream(stream)>>>(args);
-    return launch_status("acro_b200_batched_gemm");
+    return m == 64 ? launch_ring<64>(args, trans_a, trans_b, sms, as_stream(stream)) : launch_ring<32>(args, trans_a, trans_b, sms, as_stream(stream));
+}
+
+int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int op, void *stream)
+{
+    return acro_b200_batched_gemm_t(A, B, C, batch, m, n, k, 0, 0, op, stream);
 }
 
 }

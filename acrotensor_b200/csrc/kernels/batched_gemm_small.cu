@@ -1,4 +1,6 @@
 // batched_gemm, small variant: C_e = A_e * B_e for m x k by k x n matrices with m, n, k <= 16.
+// Either operand may be stored transposed (A_e as k x m, B_e as n x k): the stages keep the
+// global layout, so a transposed operand only changes the strides of the shared-memory reads.
 //
 // These products are bound by HBM (16^3: 1.3 flop per byte), so the kernel is a streaming
 // one: a persistent CTA walks over tiles of `group` consecutive matrices.  The A and B spans of
@@ -55,6 +57,7 @@ __device__ __forceinline__ void copy_async8(double *smem_dst, const double *gmem
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src) : "memory");
 }
 
+template <bool TA, bool TB>
 __global__ void __launch_bounds__(kThreads)
 batched_gemm_small_kernel(const SmallArgs a)
 {
@@ -139,19 +142,21 @@ batched_gemm_small_kernel(const SmallArgs a)
         {
             const int i0 = ib * kStrip;
             const int rows = m - i0 < kStrip ? m - i0 : kStrip;
-            const double *ar = ta + g * sa + i0 * k;
-            const double *bc = tb + g * sb + j;
+            // entry (i, kk) of A and (kk, j) of B in the stage
+            const int a_i = TA ? 1 : k, a_k = TA ? m : 1, b_k = TB ? 1 : n, b_j = TB ? k : 1;
+            const double *ar = ta + g * sa + i0 * a_i;
+            const double *bc = tb + g * sb + j * b_j;
             double *cc = sC + g * c_mat + i0 * n + j;
             double acc[kStrip];
 #pragma unroll
             for (int x = 0; x < kStrip; ++x) acc[x] = (a.op == ACRO_B200_OP_ADD && x < rows) ? cc[x * n] : 0.0;
             for (int kk = 0; kk < k; ++kk)
             {
-                const double bv = bc[kk * n];
+                const double bv = bc[kk * b_k];
 #pragma unroll
                 for (int x = 0; x < kStrip; ++x)
                 {
-                    const double av = ar[(x < rows ? x : 0) * k + kk];
+                    const double av = ar[(x < rows ? x : 0) * a_i + kk * a_k];
                     acc[x] = __dadd_rn(acc[x], __dmul_rn(av, bv));
                 }
             }
@@ -220,7 +225,8 @@ bool batched_gemm_small_supported(int m, int n, int k)
     return m >= 1 && n >= 1 && k >= 1 && m <= kMaxDim && n <= kMaxDim && k <= kMaxDim;
 }
 
-int batched_gemm_small_launch(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int op, cudaStream_t stream)
+int batched_gemm_small_launch(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int trans_a, int trans_b, int op,
+                              cudaStream_t stream)
 {
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_batched_gemm");
@@ -240,7 +246,8 @@ int batched_gemm_small_launch(const double *A, const double *B, double *C, int64
     if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_batched_gemm (status flag)");
 
     const size_t smem = static_cast<size_t>(args.group) * (kStages * (m * k + k * n) + m * n) * 8 + kStages * sizeof(uint64_t);
-    auto kernel = batched_gemm_small_kernel;
+    auto kernel = trans_a ? (trans_b ? batched_gemm_small_kernel<true, true> : batched_gemm_small_kernel<true, false>)
+                          : (trans_b ? batched_gemm_small_kernel<false, true> : batched_gemm_small_kernel<false, false>);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (status != cudaSuccess) return fail_cuda(status, "acro_b200_batched_gemm (shared memory opt-in)");
     int per_sm = static_cast<int>((200 * 1024) / (smem + 1024));

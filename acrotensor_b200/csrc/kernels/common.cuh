@@ -35,7 +35,8 @@ inline int launch_status(const char *where)
 
 // Streaming variant of batched_gemm for matrices up to 16 x 16 x 16 (batched_gemm_small.cu).
 bool batched_gemm_small_supported(int m, int n, int k);
-int batched_gemm_small_launch(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int op, cudaStream_t stream);
+int batched_gemm_small_launch(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int trans_a, int trans_b, int op,
+                              cudaStream_t stream);
 
 // Element matrix times element vector (batched_matvec.cu): form 0  Y_i = sum_k M_ik X_k, form 1  Y_j = sum_k X_k M_kj.
 bool batched_matvec_supported(int rows, int cols);

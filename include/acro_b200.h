@@ -253,6 +253,14 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
 int acro_b200_batched_gemm_supported(int m, int n, int k);
 int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k,
                            int op, void *stream);
+/* The same with either operand stored transposed: trans_a != 0 means A_e is stored k x m
+ * ("C_e_i_j = A_e_k_i B_e_k_j"), trans_b != 0 means B_e is stored n x k ("C_e_i_j = A_e_i_k B_e_j_k",
+ * e.g. the metric "G_e_m_n = J_e_m_l J_e_n_l").  A transposed operand needs m, n, k <= 64 (the kernels
+ * that stage whole matrices in shared memory; only the strides of their shared-memory reads change);
+ * the same bit-identity up to 16 and tolerance above as the plain form. */
+int acro_b200_batched_gemm_t_supported(int m, int n, int k, int trans_a, int trans_b);
+int acro_b200_batched_gemm_t(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k,
+                             int trans_a, int trans_b, int op, void *stream);
 
 /*
  * gemm:  C[M x N] (op)= A[M x K] * P[K x N], row-major fp64 with leading dimensions lda, ldp, ldc (in
