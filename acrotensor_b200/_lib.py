@@ -91,6 +91,9 @@ SIGNATURES = {
     "acro_b200_batched_gemm": (_I, [_P, _P, _P, _I64, _I, _I, _I, _I, _P]),
     "acro_b200_batched_gemm_t_supported": (_I, [_I, _I, _I, _I, _I]),
     "acro_b200_batched_gemm_t": (_I, [_P, _P, _P, _I64, _I, _I, _I, _I, _I, _I, _P]),
+    "acro_b200_gram_supported": (_I, [_I, _I]),
+    "acro_b200_gram_scratch_bytes": (_SZ, [_I, _I]),
+    "acro_b200_gram": (_I, [_P, _P, _P, _I64, _I, _I, _I, _P, _SZ, _P]),
     "acro_b200_gemm": (_I, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I, _P]),
     "acro_b200_gemm_batched": (_I, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I, _P]),
     "acro_b200_sumfact_mass_supported": (_I, [_I, _I]),

@@ -161,6 +161,13 @@ void B200Executor::Run(std::vector<Tensor *> &outputs, std::vector<std::vector<T
                           "sumfact_mass");
                 break;
             }
+            case plan::Family::Gram:
+            {
+                check_abi(acro_b200_gram(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), out->GetDeviceData(), s.rows, s.sizes[0], s.sizes[1],
+                                         s.op, Scratch, ScratchBytes, stream),
+                          "gram");
+                break;
+            }
             case plan::Family::InvariantGemm:
             {
                 const double *ptrs[ACRO_B200_MAX_INPUTS];

@@ -494,6 +494,48 @@ bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
     return true;
 }
 
+// ---------------------------------------------------------------- gram
+// S_a_b (op)= X_n_a Y_n_b: two row operands contracted over their common leading index (X and Y may be the
+// same tensor).  Rows enough to fill the machine; shorter contractions stay on the generic kernel.
+bool plan_gram(DimensionedKernel &k, int ki, Step &s)
+{
+    const Names out = k.OutputVar.IndexNames;
+    if (out.size() != 2 || !distinct(out) || k.ContractionIndexNames.size() != 1 || k.GetNumInputVars() != 2) return false;
+    const std::string n = k.ContractionIndexNames[0];
+    int xv = -1, yv = -1;
+    for (int vari = 0; vari < 2; ++vari)
+    {
+        const Names idx = indices_of(k, vari);
+        if (idx == Names{n, out[0]} && xv < 0) xv = vari;
+        else if (idx == Names{n, out[1]} && yv < 0) yv = vari;
+        else return false;
+    }
+    if (xv < 0 || yv < 0) return false;
+    const std::int64_t rows = extent_of(k, n), a = extent_of(k, out[0]), b = extent_of(k, out[1]);
+    if (a > 64 || b > 64 || !acro_b200_gram_supported(static_cast<int>(a), static_cast<int>(b))) return false;
+    if (rows < 4096 || rows * a * b < (std::int64_t(1) << 20)) return false;
+    s = Step();
+    s.family = Family::Gram;
+    s.kernels = {ki};
+    s.out.ki = ki;
+    s.op = op_code(k);
+    s.rows = rows;
+    s.sizes[0] = static_cast<int>(a);
+    s.sizes[1] = static_cast<int>(b);
+    TensorRef x, y;
+    x.ki = y.ki = ki;
+    x.vari = xv;
+    y.vari = yv;
+    s.ins = {x, y};
+    s.bytes = rows * 8 * (a + b) + a * b * 8;
+    s.flops = 2 * rows * a * b;
+    std::ostringstream note;
+    note << "Gram form over " << rows << " rows: slabs of " << ((a > 32 || b > 32) ? 64 : 32) << " rows as " << a << "x" << b
+         << " products on the fp64 tensor cores (mma.sync m8n8k4), summed per CTA, partial tiles combined in a fixed order";
+    s.note = note.str();
+    return true;
+}
+
 // ---------------------------------------------------------------- sumfact_mass
 // A kernel group is recognised by its shape, not by its names: variables and indices are
 // renamed in order of first appearance and the result is compared with the same renaming of
@@ -643,6 +685,7 @@ Step plan_single(DimensionedKernel &k, int ki)
     if (plan_rank1_gemm(k, ki, s)) return s;
     if (plan_batched_gemm(k, ki, s)) return s;
     if (plan_permute(k, ki, s)) return s;
+    if (plan_gram(k, ki, s)) return s;
     if (plan_invariant_gemm(k, ki, s)) return s;
     return plan_generic(k, ki);
 }
@@ -661,6 +704,7 @@ const char *FamilyName(Family f)
         case Family::SumfactMass: return "sumfact_mass";
         case Family::InvariantGemm: return "invariant_gemm";
         case Family::Permute: return "permute";
+        case Family::Gram: return "gram";
     }
     return "?";
 }
@@ -691,6 +735,10 @@ Program BuildProgram(DimensionedMultiKernel &mk, bool allow_elision)
         if (s.family == Family::Generic)
         {
             p.scratch_bytes = std::max(p.scratch_bytes, acro_b200_generic_scratch_bytes(&s.generic));
+        }
+        if (s.family == Family::Gram)
+        {
+            p.scratch_bytes = std::max(p.scratch_bytes, acro_b200_gram_scratch_bytes(s.sizes[0], s.sizes[1]));
         }
         if (s.family == Family::InvariantGemm)
         {

@@ -25,7 +25,8 @@ enum class Family
     BatchedGemm,
     SumfactMass,
     InvariantGemm,
-    Permute
+    Permute,
+    Gram
 };
 
 const char *FamilyName(Family f);

@@ -33,6 +33,7 @@ namespace
 
 constexpr int STAGES = 3;
 constexpr int NT = 256;               // 8 warps
+constexpr int kGramMaxParts = 1024;   // partial tiles of the Gram form: one per CTA, plus one for the last rows
 
 template <int N>
 struct Smem
@@ -255,7 +256,9 @@ __device__ __forceinline__ void issue_padded_load(Smem<N> &s, const PaddedArgs &
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&s.full[stage])) : "memory");
 }
 
-template <int N, bool TA, bool TB>
+// ACC: the products of all elements a CTA walks over are summed in its accumulators and the CTA stores one
+// m x n tile of partial sums at C + blockIdx.x * m * n when it is done (the Gram form below).
+template <int N, bool TA, bool TB, bool ACC = false>
 __global__ void __launch_bounds__(NT, N == 64 ? 1 : 4)
 batched_gemm_padded_kernel(const PaddedArgs a)
 {
@@ -286,18 +289,36 @@ batched_gemm_padded_kernel(const PaddedArgs a)
     }
     __syncthreads();
 
+    double c[MT][NTL][2];
+    bool row_live[MT], col_live[NTL];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) row_live[mt] = m0 + mt * 8 < m;
+#pragma unroll
+    for (int nt = 0; nt < NTL; ++nt) col_live[nt] = n0 + nt * 8 < n;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt) c[mt][nt][0] = c[mt][nt][1] = 0.0;
+
+    // Elements in flight ahead of the one being multiplied.  One leaves a slot of slack, so that warps may drift
+    // apart by an element; the Gram form has short elements and nothing to store per element, and fills every slot.
+    constexpr int AHEAD = ACC ? STAGES - 1 : 1;
     int64_t e = blockIdx.x;
-    if (e < a.batch) issue_padded_load(s, a, e, 0);
+#pragma unroll
+    for (int d = 0; d < AHEAD; ++d)
+    {
+        if (e + static_cast<int64_t>(d) * gridDim.x < a.batch) issue_padded_load(s, a, e + static_cast<int64_t>(d) * gridDim.x, d);
+    }
 
     int64_t it = 0;
     for (; e < a.batch; e += gridDim.x, ++it)
     {
         const int stage = static_cast<int>(it % STAGES);
-        const int64_t nxt = e + gridDim.x;
+        const int64_t nxt = e + static_cast<int64_t>(AHEAD) * gridDim.x;
         if (nxt < a.batch)
         {
-            const int ns = static_cast<int>((it + 1) % STAGES);
-            const int64_t use = (it + 1) / STAGES;
+            const int ns = static_cast<int>((it + AHEAD) % STAGES);
+            const int64_t use = (it + AHEAD) / STAGES;      // how often that slot was filled before
             if (use > 0 && !mbar_wait(&s.empty[ns], static_cast<uint32_t>((use - 1) & 1))) atomicExch(a.wait_flag, 1);
             issue_padded_load(s, a, nxt, ns);
         }
@@ -305,16 +326,13 @@ batched_gemm_padded_kernel(const PaddedArgs a)
 
         const double *sa = s.A[stage];
         const double *sb = s.B[stage];
-        double c[MT][NTL][2];
-        bool row_live[MT], col_live[NTL];
+        if (!ACC)
+        {
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) row_live[mt] = m0 + mt * 8 < m;
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < NTL; ++nt) col_live[nt] = n0 + nt * 8 < n;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int nt = 0; nt < NTL; ++nt) c[mt][nt][0] = c[mt][nt][1] = 0.0;
+                for (int nt = 0; nt < NTL; ++nt) c[mt][nt][0] = c[mt][nt][1] = 0.0;
+        }
 
         if (row_live[0] && col_live[0])
         {
@@ -336,6 +354,7 @@ batched_gemm_padded_kernel(const PaddedArgs a)
         }
         mbar_arrive(&s.empty[stage]);   // this thread no longer reads the slot
 
+        if (ACC) continue;
         double *gc = a.C + e * m * n;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
@@ -356,6 +375,37 @@ batched_gemm_padded_kernel(const PaddedArgs a)
                 }
             }
     }
+    if (ACC)
+    {
+        // this CTA's partial sums (the grid never exceeds the batch: every CTA had at least one element)
+        double *gc = a.C + static_cast<int64_t>(blockIdx.x) * m * n;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NTL; ++nt)
+            {
+                const int i = m0 + mt * 8 + g, j = n0 + nt * 8 + 2 * t;
+                if (i >= m) continue;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                {
+                    if (j + h < n) gc[i * n + j + h] = c[mt][nt][h];
+                }
+            }
+    }
+}
+
+// Sum of `parts` partial tiles (ascending order: the same bits on every run with the same grid), applied to out.
+__global__ void __launch_bounds__(256)
+gram_combine_kernel(double *__restrict__ out, const double *__restrict__ partials, int parts, int entries, int op)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= entries) return;
+    double acc = 0.0;
+    for (int p = 0; p < parts; ++p) acc = __dadd_rn(acc, __ldcg(partials + static_cast<int64_t>(p) * entries + i));
+    if (op == ACRO_B200_OP_ASSIGN) out[i] = acc;
+    else if (op == ACRO_B200_OP_ADD) out[i] = __dadd_rn(out[i], acc);
+    else out[i] = __dsub_rn(out[i], acc);
 }
 
 template <int N>
@@ -467,6 +517,80 @@ int acro_b200_batched_gemm_t(const double *A, const double *B, double *C, int64_
 int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int op, void *stream)
 {
     return acro_b200_batched_gemm_t(A, B, C, batch, m, n, k, 0, 0, op, stream);
+}
+
+// ------------------------------------------------------------------ Gram form
+// S[a, b] (op)= sum_n X[n, a] * Y[n, b]: the rows of X and Y are cut into slabs of 32 or 64; a slab is one
+// "element" of the zero-padded ring kernel with the first operand transposed (m = a, n = b, k = slab rows),
+// whose CTAs keep summing into their accumulators instead of storing a product per element.
+int acro_b200_gram_supported(int a, int b) { return (a >= 1 && b >= 1 && a <= 64 && b <= 64) ? 1 : 0; }
+
+size_t acro_b200_gram_scratch_bytes(int a, int b)
+{
+    if (!acro_b200_gram_supported(a, b)) return 0;
+    return static_cast<size_t>(kGramMaxParts) * a * b * sizeof(double);
+}
+
+int acro_b200_gram(const double *X, const double *Y, double *S, int64_t rows, int a, int b, int op, double *scratch, size_t scratch_bytes,
+                   void *stream)
+{
+    if (X == nullptr || Y == nullptr || S == nullptr || scratch == nullptr) return fail_invalid("acro_b200_gram: null argument");
+    if (rows < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_gram: bad row count or operator");
+    if (!acro_b200_gram_supported(a, b)) return fail_unsupported("acro_b200_gram: a, b must be in 1..64");
+    if (scratch_bytes < acro_b200_gram_scratch_bytes(a, b)) return fail_invalid("acro_b200_gram: scratch smaller than acro_b200_gram_scratch_bytes");
+    const int sms = sm_count();
+    if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_gram");
+    int *wait_flag = wait_flag_device_ptr();
+    if (wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_gram (status flag)");
+    cudaStream_t st = as_stream(stream);
+
+    const bool big = a > 32 || b > 32;
+    const int slab = big ? 64 : 32;
+    const int64_t slabs = rows / slab;
+    const int tail = static_cast<int>(rows - slabs * slab);
+    const int entries = a * b;
+    auto kernel = big ? batched_gemm_padded_kernel<64, true, false, true> : batched_gemm_padded_kernel<32, true, false, true>;
+    const size_t smem = big ? sizeof(Smem<64>) : sizeof(Smem<32>);
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_gram (shared memory opt-in)");
+
+    PaddedArgs pa;
+    pa.m = a;
+    pa.n = b;
+    pa.op = ACRO_B200_OP_ASSIGN;
+    pa.cols_a = a;
+    pa.cols_b = b;
+    pa.wait_flag = wait_flag;
+    int parts = 0;
+    if (slabs > 0)
+    {
+        int64_t grid = static_cast<int64_t>(sms) * (big ? 1 : 4);
+        if (grid > slabs) grid = slabs;
+        if (grid > kGramMaxParts - 1) grid = kGramMaxParts - 1;
+        pa.A = X;
+        pa.B = Y;
+        pa.C = scratch;
+        pa.batch = slabs;
+        pa.k = pa.rows_a = pa.rows_b = slab;
+        pa.wide = (aligned16(X) && aligned16(Y) && a % 2 == 0 && b % 2 == 0) ? 1 : 0;
+        kernel<<<static_cast<int>(grid), NT, smem, st>>>(pa);
+        if (cudaGetLastError() != cudaSuccess) return launch_status("acro_b200_gram");
+        parts = static_cast<int>(grid);
+    }
+    if (tail > 0)
+    {
+        pa.A = X + slabs * slab * a;
+        pa.B = Y + slabs * slab * b;
+        pa.C = scratch + static_cast<int64_t>(parts) * entries;
+        pa.batch = 1;
+        pa.k = pa.rows_a = pa.rows_b = tail;
+        pa.wide = (aligned16(pa.A) && aligned16(pa.B) && a % 2 == 0 && b % 2 == 0) ? 1 : 0;
+        kernel<<<1, NT, smem, st>>>(pa);
+        if (cudaGetLastError() != cudaSuccess) return launch_status("acro_b200_gram (last rows)");
+        ++parts;
+    }
+    gram_combine_kernel<<<(entries + 255) / 256, 256, 0, st>>>(S, scratch, parts, entries, op);
+    return launch_status("acro_b200_gram (combine)");
 }
 
 }

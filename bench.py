@@ -621,6 +621,9 @@ def run_ops(args):
             ("batched_gemm_27_transposed", "C_e_i_j = A_e_k_i B_e_j_k", lambda n: [(n, 27, 27), (n, 27, 27), (n, 27, 27)], 1 << 17),
             ("batched_gemm_64", "C_e_i_j = A_e_i_k B_e_k_j", lambda n: [(n, 64, 64), (n, 64, 64), (n, 64, 64)], 1 << 14),
             ("batched_gemm_64_transposed", "C_e_i_j = A_e_k_i B_e_j_k", lambda n: [(n, 64, 64), (n, 64, 64), (n, 64, 64)], 1 << 14),
+            ("gram_8", "S_a_b = X_n_a Y_n_b", lambda n: [(8, 8), (n, 8), (n, 8)], 1 << 23),
+            ("gram_27", "S_a_b = X_n_a Y_n_b", lambda n: [(27, 27), (n, 27), (n, 27)], 1 << 21),
+            ("gram_64", "S_a_b = X_n_a Y_n_b", lambda n: [(64, 64), (n, 64), (n, 64)], 1 << 20),
             ("batched_matvec_27", "Y_e_i = M_e_i_j X_e_j", lambda n: [(n, 27), (n, 27, 27), (n, 27)], 1 << 18),
             ("batched_matvec_64", "Y_e_i = M_e_i_j X_e_j", lambda n: [(n, 64), (n, 64, 64), (n, 64)], 1 << 15)]:
         n = max(64, int(full * args.scale))

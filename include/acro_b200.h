@@ -263,6 +263,21 @@ int acro_b200_batched_gemm_t(const double *A, const double *B, double *C, int64_
                              int trans_a, int trans_b, int op, void *stream);
 
 /*
+ * gram:  S[a,b] (op)= sum_{n} X[n,a] * Y[n,b]  ("S_a_b = X_n_a Y_n_b": normal equations, Gram matrices,
+ * moments), a, b <= 64, any number of rows.  X and Y are read once: slabs of 32 (64 when a or b exceeds 32)
+ * rows go through the batched_gemm ring as products X_slab^T * Y_slab on the fp64 tensor cores, every
+ * CTA keeps summing into its accumulators, writes one a x b tile of partial sums to `scratch`
+ * (acro_b200_gram_scratch_bytes) and a second kernel adds the tiles in ascending order: the same bits
+ * on every run on the same device, within tolerance of the reference's sequential sum.
+ * HBM traffic 8*(a + b) bytes and 2ab flops per row.  The generated kernel of the reference runs one
+ * thread per entry of S over all rows (exec/CudaExecutor.cpp:520-604).
+ */
+int acro_b200_gram_supported(int a, int b);
+size_t acro_b200_gram_scratch_bytes(int a, int b);
+int acro_b200_gram(const double *X, const double *Y, double *S, int64_t rows, int a, int b, int op,
+                   double *scratch, size_t scratch_bytes, void *stream);
+
+/*
  * gemm:  C[M x N] (op)= A[M x K] * P[K x N], row-major fp64 with leading dimensions lda, ldp, ldc (in
  * doubles), on the fp64 tensor cores: 64 x 64 tiles, K walked in slabs of 64 through a three-slot
  * asynchronous copy ring.  The engine uses it for contractions in which exactly one input carries the
