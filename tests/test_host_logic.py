@@ -288,6 +288,17 @@ def test_planner_routes_sizes_and_layouts_to_the_expected_variants():
     assert "3-stage asynchronous bulk-copy ring" in step0(gemm, (10, 64, 64), (10, 64, 64), (10, 64, 64))
     assert "64x64 tiles of every product" in step0(gemm, (10, 48, 48), (10, 48, 48), (10, 48, 48))
     assert "64x64 tiles of every product" in step0(gemm, (4, 125, 100), (4, 125, 90), (4, 90, 100))
+    # an operand stored transposed stays in the family up to 64; the input that carries i is the left factor
+    assert "(first operand stored transposed)" in step0("C_e_i_j = A_e_k_i B_e_k_j", (10, 64, 64), (10, 64, 64), (10, 64, 64))
+    line = step0("C_e_i_j = A_e_j_k B_e_k_i", (10, 9, 6), (10, 6, 7), (10, 7, 9))
+    assert "family=batched_gemm" in line and "9x7 by 7x6" in line and "(first operand" in line and "(second operand" in line
+    assert "zero-padded on chip to 64" in step0("C_e_i_j = A_e_i_k B_e_j_k", (10, 40, 24), (10, 40, 30), (10, 24, 30))
+    assert "family=generic" in step0("C_e_i_j = A_e_i_k B_e_j_k", (10, 70, 24), (10, 70, 30), (10, 24, 30))
+    # two row operands contracted over a long common leading index
+    assert "family=gram" in step0("S_a_b = X_n_a Y_n_b", (27, 27), (100000, 27), (100000, 27))
+    assert "family=gram" in step0("S_a_b += Y_n_b X_n_a", (5, 9), (100000, 9), (100000, 5))
+    assert "family=generic" in step0("S_a_b = X_n_a Y_n_b", (27, 27), (1000, 27), (1000, 27))
+    assert "family=generic" in step0("S_a_b = X_n_a Y_n_b", (65, 8), (100000, 65), (100000, 8))
     # index reorderings: a tiled transpose only when the fastest index changes and both runs are long enough
     assert "family=permute" in step0("A_i_j=B_j_i", (300, 400), (400, 300))
     assert "family=permute" in step0("A_e_i_j = B_e_j_i", (3000, 27, 27), (3000, 27, 27))
