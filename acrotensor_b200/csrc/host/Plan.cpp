@@ -530,8 +530,10 @@ bool plan_gram(DimensionedKernel &k, int ki, Step &s)
     s.bytes = rows * 8 * (a + b) + a * b * 8;
     s.flops = 2 * rows * a * b;
     std::ostringstream note;
-    note << "Gram form over " << rows << " rows: slabs of " << ((a > 32 || b > 32) ? 64 : 32) << " rows as " << a << "x" << b
-         << " products on the fp64 tensor cores (mma.sync m8n8k4), summed per CTA, partial tiles combined in a fixed order";
+    note << "Gram form over " << rows << " rows: ";
+    if (a <= 16 && b <= 16) note << "tiles of rows streamed through shared memory (bulk copies), 4x4 blocks of the " << a << "x" << b << " result in registers";
+    else note << "slabs of " << ((a > 32 || b > 32) ? 64 : 32) << " rows as " << a << "x" << b << " products on the fp64 tensor cores (mma.sync m8n8k4)";
+    note << ", summed per CTA, partial tiles combined in a fixed order";
     s.note = note.str();
     return true;
 }

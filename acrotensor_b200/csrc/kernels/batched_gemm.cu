@@ -520,7 +520,8 @@ int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t 
 }
 
 // ------------------------------------------------------------------ Gram form
-// S[a, b] (op)= sum_n X[n, a] * Y[n, b]: the rows of X and Y are cut into slabs of 32 or 64; a slab is one
+// S[a, b] (op)= sum_n X[n, a] * Y[n, b].  Up to 16 x 16 the streaming kernel of gram_stream.cu; above that
+// the rows of X and Y are cut into slabs of 32 or 64; a slab is one
 // "element" of the zero-padded ring kernel with the first operand transposed (m = a, n = b, k = slab rows),
 // whose CTAs keep summing into their accumulators instead of storing a product per element.
 int acro_b200_gram_supported(int a, int b) { return (a >= 1 && b >= 1 && a <= 64 && b <= 64) ? 1 : 0; }
@@ -543,12 +544,22 @@ int acro_b200_gram(const double *X, const double *Y, double *S, int64_t rows, in
     int *wait_flag = wait_flag_device_ptr();
     if (wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_gram (status flag)");
     cudaStream_t st = as_stream(stream);
+    const int entries = a * b;
+
+    if (gram_stream_supported(a, b))
+    {
+        // a, b <= 16: bound by HBM, streamed with plain fused multiply-adds (gram_stream.cu)
+        int tiles_written = 0;
+        const int rc = gram_stream_launch(X, Y, scratch, rows, a, b, kGramMaxParts, &tiles_written, st);
+        if (rc != ACRO_B200_OK) return rc;
+        gram_combine_kernel<<<(entries + 255) / 256, 256, 0, st>>>(S, scratch, tiles_written, entries, op);
+        return launch_status("acro_b200_gram (combine)");
+    }
 
     const bool big = a > 32 || b > 32;
     const int slab = big ? 64 : 32;
     const int64_t slabs = rows / slab;
     const int tail = static_cast<int>(rows - slabs * slab);
-    const int entries = a * b;
     auto kernel = big ? batched_gemm_padded_kernel<64, true, false, true> : batched_gemm_padded_kernel<32, true, false, true>;
     const size_t smem = big ? sizeof(Smem<64>) : sizeof(Smem<32>);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

@@ -42,6 +42,11 @@ int batched_gemm_small_launch(const double *A, const double *B, double *C, int64
 bool batched_matvec_supported(int rows, int cols);
 int batched_matvec_launch(const double *M, const double *X, double *Y, int64_t batch, int rows, int cols, int form, int op, cudaStream_t stream);
 
+// Streaming variant of the Gram form for a, b <= 16 (gram_stream.cu): one a x b tile of partial sums per CTA at
+// partials, *parts = number of tiles written (at most max_parts).
+bool gram_stream_supported(int a, int b);
+int gram_stream_launch(const double *X, const double *Y, double *partials, int64_t rows, int a, int b, int max_parts, int *parts, cudaStream_t stream);
+
 __host__ __device__ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }

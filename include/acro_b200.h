@@ -264,11 +264,13 @@ int acro_b200_batched_gemm_t(const double *A, const double *B, double *C, int64_
 
 /*
  * gram:  S[a,b] (op)= sum_{n} X[n,a] * Y[n,b]  ("S_a_b = X_n_a Y_n_b": normal equations, Gram matrices,
- * moments), a, b <= 64, any number of rows.  X and Y are read once: slabs of 32 (64 when a or b exceeds 32)
- * rows go through the batched_gemm ring as products X_slab^T * Y_slab on the fp64 tensor cores, every
- * CTA keeps summing into its accumulators, writes one a x b tile of partial sums to `scratch`
- * (acro_b200_gram_scratch_bytes) and a second kernel adds the tiles in ascending order: the same bits
- * on every run on the same device, within tolerance of the reference's sequential sum.
+ * moments), a, b <= 64, any number of rows.  X and Y are read once.  a, b <= 16 (bound by HBM): tiles of
+ * rows arrive by bulk copies, a thread keeps a 4 x 4 block of S in registers over its share of the rows.
+ * Larger: slabs of 32 (64 when a or b exceeds 32) rows go through the batched_gemm ring as products
+ * X_slab^T * Y_slab on the fp64 tensor cores and every CTA keeps summing into its accumulators.  Either
+ * way a CTA writes one a x b tile of partial sums to `scratch` (acro_b200_gram_scratch_bytes) and a
+ * second kernel adds the tiles in ascending order: the same bits on every run on the same device,
+ * within tolerance of the reference's sequential sum.
  * HBM traffic 8*(a + b) bytes and 2ab flops per row.  The generated kernel of the reference runs one
  * thread per entry of S over all rows (exec/CudaExecutor.cpp:520-604).
  */

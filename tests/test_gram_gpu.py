@@ -1,6 +1,7 @@
 """GPU parity of the Gram form S_a_b (op)= X_n_a Y_n_b (two row operands contracted over their common
-leading index), through the kernel layer of the C ABI and through the engine.  The slabs of rows are
-summed on the fp64 tensor cores and per CTA, so the order differs from the reference's sequential sum:
+leading index), through the kernel layer of the C ABI and through the engine.  Rows are summed per
+thread and per CTA (up to 16 x 16: streaming kernel with fused multiply-add; above: slabs of rows on
+the fp64 tensor cores), so the order differs from the reference's sequential sum:
 |gpu - ref| <= 1e-12 * sum|terms|; two runs give the same bits."""
 import ctypes
 
@@ -33,6 +34,7 @@ def to_dev(torch, arr, offset=0):
 @pytest.mark.parametrize("rows,a,b,op,offset", [
     (64 * 500, 64, 64, 0, 0), (64 * 500 + 37, 64, 64, 1, 0), (70001, 40, 64, 2, 0), (9999, 33, 7, 0, 1), (50, 64, 64, 0, 0),
     (32 * 3000, 8, 8, 0, 0), (100003, 8, 8, 1, 0), (100000, 5, 9, 2, 0), (77777, 27, 27, 0, 1), (31, 8, 8, 0, 0), (32, 16, 3, 0, 0),
+    (77777, 16, 16, 0, 1), (50001, 6, 10, 0, 0), (70000, 13, 4, 1, 0), (2049, 16, 16, 2, 0), (600000, 2, 1, 0, 0),
     (200001, 1, 1, 0, 0), (150000, 32, 1, 1, 0), (150000, 2, 32, 0, 1), (1, 3, 3, 0, 0), (400000, 3, 3, 0, 0)])
 def test_gram_kernel(torch, rows, a, b, op, offset):
     rng = np.random.default_rng(rows + a + 3 * b)
