@@ -48,6 +48,11 @@ REFERENCE_TEST_CASES = [
     ("long_two_loop_sums", [("S_a_b += X_n_m_a Y_m_n_b W_m", "S", ["X", "Y", "W"])],
      {"S": (2, 3), "X": (300, 70, 2), "Y": (70, 300, 3), "W": (70,)}, False),
     ("pointwise_noscalar", [("D_p_m_n = X_p_m_l X_p_n_l", "D", ["X", "X"])], {"D": (300, 3, 3), "X": (300, 3, 3)}, False),
+    # element products with both operands stored transposed; Gram forms (the same tensor twice; accumulate)
+    ("batched_matmul_transposed", [("C_e_i_j = A_e_k_i B_e_j_k", "C", ["A", "B"])],
+     {"C": (10, 5, 4), "A": (10, 6, 5), "B": (10, 4, 6)}, False),
+    ("gram_normal_equations", [("S_a_b = X_n_a X_n_b", "S", ["X", "X"])], {"S": (6, 6), "X": (30000, 6)}, False),
+    ("gram_accumulate", [("S_a_b += X_n_a Y_n_b", "S", ["X", "Y"])], {"S": (20, 24), "X": (4500, 20), "Y": (4500, 24)}, False),
 ]
 
 SMALL_BATCH = {"cfg0": 1000, "cfg1": 6, "cfg2": 9, "cfg3": 7, "cfg4": 2}
