@@ -10,8 +10,8 @@ mirror of that API over the C ABI, used by the tests and the benchmark:
     >>> TE("S_i_j = A_n_i_j B_n", S, A, B); S.MoveFromGPU()
 """
 from ._lib import AcroError, build, lib, LIB_PATH
-from .host import (IndexMapping, PeerGroup, SharedEntryExchange, SliceTensor, Tensor, TensorEngine, describe_kernel, describe_plan, device_count,
-                   isCudaReady, set_stream)
+from .host import (IndexMapping, PeerGroup, SharedEntryExchange, SlabTensor, SliceTensor, Tensor, TensorEngine, batch_slab, describe_kernel,
+                   describe_plan, device_count, isCudaReady, set_stream)
 
-__all__ = ["AcroError", "IndexMapping", "PeerGroup", "SharedEntryExchange", "SliceTensor", "Tensor", "TensorEngine", "build", "describe_kernel", "describe_plan",
+__all__ = ["AcroError", "IndexMapping", "PeerGroup", "SharedEntryExchange", "SlabTensor", "SliceTensor", "Tensor", "TensorEngine", "batch_slab", "build", "describe_kernel", "describe_plan",
            "device_count", "isCudaReady", "lib", "set_stream", "LIB_PATH"]

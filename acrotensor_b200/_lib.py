@@ -17,6 +17,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT = 0, -1, -2, -3, -4
 MAX_LOOPS, MAX_INPUTS, MAX_POINT_LOOPS, MAX_SCALARS = 24, 12, 6, 6
 MAX_PEERS, IPC_HANDLE_BYTES = 16, 64
 OP_ASSIGN, OP_ADD, OP_SUB = 0, 1, 2
+SCRATCH_READY = 0x100
 
 
 class AcroError(RuntimeError):
@@ -80,6 +81,7 @@ SIGNATURES = {
     "acro_b200_peer_group_world": (_I, [_P]),
     "acro_b200_peer_group_is_connected": (_I, [_P]),
     "acro_b200_reduce_batch_allreduce": (_I, [_P, _P, _P, _I64, _I, _I, _P, _SZ, _P, _P]),
+    "acro_b200_peer_allreduce": (_I, [_P, _P, _I64, _I, _P, _P]),
     "acro_engine_set_peer_group": (_I, [_P, _P]),
     "acro_b200_reduce_batch_noalloc_max_f": (_I, []),
     "acro_b200_reduce_batch_noalloc": (_I, [_P, _P, _P, _I64, _I, _I, _P]),
@@ -145,6 +147,10 @@ SIGNATURES = {
     "acro_tensor_reshape": (_I, [_P, _I, ctypes.POINTER(_I)]),
     "acro_tensor_retarget": (_I, [_P, _P, _P]),
     "acro_tensor_set_transient": (_I, [_P, _I]),
+    "acro_b200_batch_slab": (_I, [_I64, _I, _I, ctypes.POINTER(_I64), ctypes.POINTER(_I64)]),
+    "acro_tensor_slab": (_I, [_P, _I64, _I64, ctypes.POINTER(_P)]),
+    "acro_tensor_set_sharded": (_I, [_P, _I]),
+    "acro_tensor_is_sharded": (_I, [_P]),
     "acro_engine_create": (_I, [_S, ctypes.POINTER(_P)]),
     "acro_engine_destroy": (_I, [_P]),
     "acro_engine_set_executor_type": (_I, [_P, _S]),

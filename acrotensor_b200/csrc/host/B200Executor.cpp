@@ -27,7 +27,8 @@ Tensor *resolve(const plan::TensorRef &r, std::vector<Tensor *> &outputs, std::v
 }
 
 B200Executor::B200Executor(DimensionedMultiKernel *multi_kernel)
-    : KernelExecutor(multi_kernel), Scratch(nullptr), ScratchBytes(0)
+    : KernelExecutor(multi_kernel), Scratch(nullptr), ScratchBytes(0), ReduceScratch(nullptr), ReduceScratchBytes(0), RankSum(nullptr),
+      RankSumBytes(0)
 {
     Unfused.reset(new plan::Program(plan::BuildProgram(*MultiKernel, false)));
     Fused.reset(new plan::Program(plan::BuildProgram(*MultiKernel, true)));
@@ -36,6 +37,24 @@ B200Executor::B200Executor(DimensionedMultiKernel *multi_kernel)
 B200Executor::~B200Executor()
 {
     if (Scratch != nullptr) cudaFree(Scratch);
+    if (ReduceScratch != nullptr) cudaFree(ReduceScratch);
+    if (RankSum != nullptr) cudaFree(RankSum);
+}
+
+namespace
+{
+// Grows a device buffer owned by the executor (contents are not kept).
+void reserve(double *&buffer, std::size_t &have, std::size_t need)
+{
+    if (need <= have) return;
+    if (buffer != nullptr) acroCudaErrorCheck(cudaFree(buffer));
+    buffer = nullptr;
+    have = 0;
+    void *p = nullptr;
+    acroCudaErrorCheck(cudaMalloc(&p, need));
+    buffer = static_cast<double *>(p);
+    have = need;
+}
 }
 
 std::string B200Executor::GetImplementation()
@@ -80,52 +99,78 @@ void B200Executor::Run(std::vector<Tensor *> &outputs, std::vector<std::vector<T
     }
 
     void *stream = Stream();
-    if (program->scratch_bytes > ScratchBytes)
-    {
-        if (Scratch != nullptr) acroCudaErrorCheck(cudaFree(Scratch));
-        Scratch = nullptr;
-        void *p = nullptr;
-        acroCudaErrorCheck(cudaMalloc(&p, program->scratch_bytes));
-        Scratch = static_cast<double *>(p);
-        ScratchBytes = program->scratch_bytes;
-    }
+    reserve(Scratch, ScratchBytes, program->scratch_bytes);
+    acro_b200_peer_group *group = static_cast<acro_b200_peer_group *>(ThePeerGroup);
 
-    for (const plan::Step &s : program->steps)
+    for (const plan::Step &planned : program->steps)
     {
-        Tensor *out = resolve(s.out, outputs, inputs);
+        Tensor *out = resolve(planned.out, outputs, inputs);
         std::vector<Tensor *> ins;
-        for (const plan::TensorRef &r : s.ins) ins.push_back(resolve(r, outputs, inputs));
+        for (const plan::TensorRef &r : planned.ins) ins.push_back(resolve(r, outputs, inputs));
 
         // Bring operands to the device (allocating / copying only where the host side is
         // fresh).  A "=" output is overwritten, so its old contents are not uploaded,
         // unless it is a slice: its parent holds other entries that must survive.
-        if (s.op == ACRO_B200_OP_ASSIGN && !out->IsOnGPU() && dynamic_cast<SliceTensor *>(out) == nullptr) out->SwitchToGPU();
+        if (planned.op == ACRO_B200_OP_ASSIGN && !out->IsOnGPU() && dynamic_cast<SliceTensor *>(out) == nullptr) out->SwitchToGPU();
         MoveTensorsToGPU(out, ins);
+
+        // Multi-GPU: when an input whose leading index is contracted is this rank's slab of a sharded
+        // tensor, the kernel leaves a partial sum on every rank and the result is their sum.  reduce_batch
+        // exchanges inside its own kernel; every other family is followed by the all-reduce kernel.  With
+        // "+=" / "-=" the partial sum goes to a buffer of its own first, so that the old contents of the
+        // output are counted once and not once per rank.
+        bool sum_over_ranks = false;
+        if (group != nullptr)
+        {
+            for (const plan::TensorRef &r : planned.lead_contracted) sum_over_ranks = sum_over_ranks || resolve(r, outputs, inputs)->IsSharded();
+        }
+        const bool fused_rank_sum = sum_over_ranks && planned.family == plan::Family::ReduceBatch;
+        const bool separate_rank_sum = sum_over_ranks && !fused_rank_sum;
+        const bool to_buffer = separate_rank_sum && planned.op != ACRO_B200_OP_ASSIGN;
+        plan::Step redirected;
+        double *out_data = out->GetDeviceData();
+        if (to_buffer)
+        {
+            redirected = planned;
+            redirected.op = redirected.generic.op = redirected.pointwise.op = ACRO_B200_OP_ASSIGN;
+            redirected.zero_fill_first = (planned.family == plan::Family::Generic);
+            reserve(RankSum, RankSumBytes, out->GetByteSize());
+            out_data = RankSum;
+        }
+        const plan::Step &s = to_buffer ? redirected : planned;
+        const std::int64_t out_size = out->GetSize64();
 
         switch (s.family)
         {
             case plan::Family::Generic:
             {
-                if (s.zero_fill_first) check_abi(acro_b200_fill(out->GetDeviceData(), out->GetSize64(), 0.0, stream), "fill");
+                if (s.zero_fill_first) check_abi(acro_b200_fill(out_data, out_size, 0.0, stream), "fill");
                 const double *ptrs[ACRO_B200_MAX_INPUTS];
                 for (std::size_t i = 0; i < ins.size(); ++i) ptrs[i] = ins[i]->GetDeviceData();
-                check_abi(acro_b200_generic_launch(&s.generic, out->GetDeviceData(), ptrs, Scratch, ScratchBytes, stream), "generic_launch");
+                check_abi(acro_b200_generic_launch(&s.generic, out_data, ptrs, Scratch, ScratchBytes, stream), "generic_launch");
                 break;
             }
             case plan::Family::ReduceBatch:
             {
                 const double *w = ins.size() > 1 ? ins[1]->GetDeviceData() : nullptr;
-                if (ThePeerGroup != nullptr)
+                // A buffer of its own for the ticket counter and the CTA partial sums: zeroed once here, left
+                // zeroed by every launch, touched by nothing else, so no clear precedes the launches.
+                const std::size_t need = acro_b200_reduce_batch_scratch_bytes(s.sizes[0]);
+                if (need > ReduceScratchBytes)
                 {
-                    // the batch index is sharded over the ranks of the group: fused all-reduce
-                    check_abi(acro_b200_reduce_batch_allreduce(ins[0]->GetDeviceData(), w, out->GetDeviceData(), s.rows, s.sizes[0], s.op,
-                                                               Scratch, ScratchBytes, static_cast<acro_b200_peer_group *>(ThePeerGroup), stream),
+                    reserve(ReduceScratch, ReduceScratchBytes, need);
+                    acroCudaErrorCheck(cudaMemsetAsync(ReduceScratch, 0, 256, static_cast<cudaStream_t>(stream)));
+                }
+                if (fused_rank_sum)
+                {
+                    check_abi(acro_b200_reduce_batch_allreduce(ins[0]->GetDeviceData(), w, out_data, s.rows, s.sizes[0], s.op | ACRO_B200_SCRATCH_READY,
+                                                               ReduceScratch, ReduceScratchBytes, group, stream),
                               "reduce_batch_allreduce");
                 }
                 else
                 {
-                    check_abi(acro_b200_reduce_batch(ins[0]->GetDeviceData(), w, out->GetDeviceData(), s.rows, s.sizes[0], s.op,
-                                                     Scratch, ScratchBytes, stream),
+                    check_abi(acro_b200_reduce_batch(ins[0]->GetDeviceData(), w, out_data, s.rows, s.sizes[0], s.op | ACRO_B200_SCRATCH_READY,
+                                                     ReduceScratch, ReduceScratchBytes, stream),
                               "reduce_batch");
                 }
                 break;
@@ -136,20 +181,20 @@ void B200Executor::Run(std::vector<Tensor *> &outputs, std::vector<std::vector<T
                 const double *scalars[ACRO_B200_MAX_SCALARS] = {nullptr};
                 for (int i = 0; i < ns; ++i) scalars[i] = ins[i]->GetDeviceData();
                 check_abi(acro_b200_pointwise_sym(&s.pointwise, scalars, ins[ns]->GetDeviceData(), ins[ns + 1]->GetDeviceData(),
-                                                  out->GetDeviceData(), stream),
+                                                  out_data, stream),
                           "pointwise_sym");
                 break;
             }
             case plan::Family::Rank1Gemm:
             {
                 check_abi(acro_b200_rank1_gemm(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), ins[2]->GetDeviceData(),
-                                               out->GetDeviceData(), s.rows, s.sizes[0], s.sizes[1], s.sizes[2], s.op, stream),
+                                               out_data, s.rows, s.sizes[0], s.sizes[1], s.sizes[2], s.op, stream),
                           "rank1_gemm");
                 break;
             }
             case plan::Family::BatchedGemm:
             {
-                check_abi(acro_b200_batched_gemm_t(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), out->GetDeviceData(), s.rows,
+                check_abi(acro_b200_batched_gemm_t(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), out_data, s.rows,
                                                    s.sizes[0], s.sizes[1], s.sizes[2], s.sizes[3], s.sizes[4], s.op, stream),
                           "batched_gemm");
                 break;
@@ -157,13 +202,13 @@ void B200Executor::Run(std::vector<Tensor *> &outputs, std::vector<std::vector<T
             case plan::Family::SumfactMass:
             {
                 check_abi(acro_b200_sumfact_mass(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), ins[2]->GetDeviceData(),
-                                                 out->GetDeviceData(), s.rows, s.sizes[0], s.sizes[1], stream),
+                                                 out_data, s.rows, s.sizes[0], s.sizes[1], stream),
                           "sumfact_mass");
                 break;
             }
             case plan::Family::Gram:
             {
-                check_abi(acro_b200_gram(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), out->GetDeviceData(), s.rows, s.sizes[0], s.sizes[1],
+                check_abi(acro_b200_gram(ins[0]->GetDeviceData(), ins[1]->GetDeviceData(), out_data, s.rows, s.sizes[0], s.sizes[1],
                                          s.op, Scratch, ScratchBytes, stream),
                           "gram");
                 break;
@@ -173,18 +218,22 @@ void B200Executor::Run(std::vector<Tensor *> &outputs, std::vector<std::vector<T
                 const double *ptrs[ACRO_B200_MAX_INPUTS];
                 for (std::size_t i = 1; i < ins.size(); ++i) ptrs[i - 1] = ins[i]->GetDeviceData();
                 check_abi(acro_b200_generic_launch(&s.generic, Scratch, ptrs, nullptr, 0, stream), "generic_launch (invariant product)");
-                check_abi(acro_b200_gemm(ins[0]->GetDeviceData(), Scratch, out->GetDeviceData(), s.rows, s.sizes[1], s.sizes[0], s.sizes[0],
+                check_abi(acro_b200_gemm(ins[0]->GetDeviceData(), Scratch, out_data, s.rows, s.sizes[1], s.sizes[0], s.sizes[0],
                                          s.sizes[2], s.sizes[1], s.op, stream),
                           "gemm");
                 break;
             }
             case plan::Family::Permute:
             {
-                check_abi(acro_b200_permute(&s.generic, out->GetDeviceData(), ins[0]->GetDeviceData(), stream), "permute");
+                check_abi(acro_b200_permute(&s.generic, out_data, ins[0]->GetDeviceData(), stream), "permute");
                 break;
             }
             default:
                 ACROBATIC_ASSERT(false, "Planned a kernel family that is not built into this library.");
+        }
+        if (separate_rank_sum)
+        {
+            check_abi(acro_b200_peer_allreduce(out->GetDeviceData(), out_data, out_size, planned.op, group, stream), "peer_allreduce");
         }
     }
 }

@@ -676,7 +676,7 @@ bool plan_permute(DimensionedKernel &k, int ki, Step &s)
     return true;
 }
 
-Step plan_single(DimensionedKernel &k, int ki)
+Step plan_family(DimensionedKernel &k, int ki)
 {
     Step s;
     // debugging aid: ACRO_B200_ONLY_GENERIC=1 in the environment plans every kernel on the generic family
@@ -690,6 +690,23 @@ Step plan_single(DimensionedKernel &k, int ki)
     if (plan_gram(k, ki, s)) return s;
     if (plan_invariant_gemm(k, ki, s)) return s;
     return plan_generic(k, ki);
+}
+
+Step plan_single(DimensionedKernel &k, int ki)
+{
+    Step s = plan_family(k, ki);
+    // Whatever family runs it: which inputs would, as a rank's slab, leave this rank with a partial sum only?
+    for (int vari = 0; vari < k.GetNumInputVars(); ++vari)
+    {
+        const Names idx = indices_of(k, vari);
+        if (idx.empty()) continue;
+        if (std::find(k.ContractionIndexNames.begin(), k.ContractionIndexNames.end(), idx[0]) == k.ContractionIndexNames.end()) continue;
+        TensorRef r;
+        r.ki = ki;
+        r.vari = vari;
+        s.lead_contracted.push_back(r);
+    }
+    return s;
 }
 
 }  // namespace
@@ -770,6 +787,12 @@ std::string Program::Describe(DimensionedMultiKernel &mk) const
         os << "step " << i << ": family=" << FamilyName(s.family) << " kernels=";
         for (std::size_t j = 0; j < s.kernels.size(); ++j) os << (j ? "," : "") << s.kernels[j];
         os << " bytes=" << s.bytes << " flops=" << s.flops << " | " << s.note << "\n";
+        if (!s.lead_contracted.empty())
+        {
+            os << "        summed over the ranks of a peer group when one of these inputs is a rank's slab:";
+            for (const TensorRef &r : s.lead_contracted) os << " " << mk.Kernels[r.ki]->GetVarName(r.vari);
+            os << (s.family == Family::ReduceBatch ? " (all-reduce fused into the kernel)" : " (all-reduce kernel after the step)") << "\n";
+        }
     }
     if (scratch_bytes) os << "scratch: " << scratch_bytes << " bytes\n";
     return os.str();

@@ -56,6 +56,9 @@ struct Step
     std::int64_t rows = 0;           // reduce_batch / batch count of the GEMM families
     int sizes[5] = {0, 0, 0, 0, 0};  // family-specific sizes and flags
     std::vector<TensorRef> elided;   // transient outputs this step keeps on chip
+    // Inputs whose leading (slowest) index is contracted.  When the engine has a peer group and one of
+    // these tensors is a rank's slab (Tensor::IsSharded), the step's result is summed over the ranks.
+    std::vector<TensorRef> lead_contracted;
 };
 
 struct Program

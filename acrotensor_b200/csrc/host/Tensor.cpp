@@ -20,7 +20,7 @@ void check_abi(int status)
 
 Tensor::Tensor()
     : Size(0), Initialized(false), OwnsData(false), OwnsDeviceData(false), MappedToGPU(false), OnGPU(false),
-      Transient(false), Data(nullptr), DeviceData(nullptr)
+      Transient(false), Sharded(false), Data(nullptr), DeviceData(nullptr)
 {
 }
 

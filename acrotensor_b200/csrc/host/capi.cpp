@@ -179,6 +179,39 @@ int acro_tensor_set_transient(acro_tensor *t, int transient)
     });
 }
 
+int acro_b200_batch_slab(int64_t batch, int rank, int world, int64_t *begin, int64_t *end)
+{
+    if (begin == nullptr || end == nullptr || batch < 0 || world < 1 || rank < 0 || rank >= world)
+    {
+        acro_b200_detail::set_last_error("acro_b200_batch_slab: need batch >= 0, 0 <= rank < world and result pointers");
+        return ACRO_B200_EINVAL;
+    }
+    // 128-bit products: batch * world may pass 2^63
+    *begin = static_cast<int64_t>(static_cast<__int128>(batch) * rank / world);
+    *end = static_cast<int64_t>(static_cast<__int128>(batch) * (rank + 1) / world);
+    return ACRO_B200_OK;
+}
+
+int acro_tensor_slab(acro_tensor *parent, int64_t begin, int64_t end, acro_tensor **out)
+{
+    return guarded([&] {
+        if (parent == nullptr || out == nullptr) acro::throw_error("acro_tensor_slab: bad arguments");
+        std::unique_ptr<acro_tensor> h(new acro_tensor);
+        h->t.reset(new acro::SlabTensor(*parent->t, begin, end));
+        *out = h.release();
+    });
+}
+
+int acro_tensor_set_sharded(acro_tensor *t, int sharded)
+{
+    return guarded([&] {
+        if (t == nullptr) acro::throw_error("acro_tensor_set_sharded: null tensor handle");
+        t->t->SetSharded(sharded != 0);
+    });
+}
+
+int acro_tensor_is_sharded(const acro_tensor *t) { return t ? (t->t->IsSharded() ? 1 : 0) : ACRO_B200_EINVAL; }
+
 int acro_engine_create(const char *exec_type, acro_engine **out)
 {
     return guarded([&] {

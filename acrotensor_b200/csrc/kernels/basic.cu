@@ -2,6 +2,7 @@
 #include "common.cuh"
 #include "tma.cuh"
 
+#include <atomic>
 #include <dlfcn.h>
 #include <mutex>
 #include <string>
@@ -60,10 +61,13 @@ namespace
 constexpr int kMaxDevices = 64;
 std::mutex g_wait_flag_lock;
 int *g_wait_flag_of_device[kMaxDevices] = {nullptr};
+std::atomic<unsigned long long> g_context_epoch{0};
 }
 
 namespace acro_b200_detail
 {
+unsigned long long context_epoch() { return g_context_epoch.load(); }
+
 int *wait_flag_device_ptr()
 {
     std::mutex &lock = g_wait_flag_lock;
@@ -143,6 +147,7 @@ int acro_b200_set_context(void *cuda_context)
     }
     std::lock_guard<std::mutex> guard(g_wait_flag_lock);
     for (int d = 0; d < kMaxDevices; ++d) g_wait_flag_of_device[d] = nullptr;
+    ++g_context_epoch;      // every other cached device-symbol address is stale too
     return ACRO_B200_OK;
 }
 

@@ -585,7 +585,8 @@ int acro_b200_gram(const double *X, const double *Y, double *S, int64_t rows, in
         pa.k = pa.rows_a = pa.rows_b = slab;
         pa.wide = (aligned16(X) && aligned16(Y) && a % 2 == 0 && b % 2 == 0) ? 1 : 0;
         kernel<<<static_cast<int>(grid), NT, smem, st>>>(pa);
-        if (cudaGetLastError() != cudaSuccess) return launch_status("acro_b200_gram");
+        const int launched = launch_status("acro_b200_gram");
+        if (launched != ACRO_B200_OK) return launched;
         parts = static_cast<int>(grid);
     }
     if (tail > 0)
@@ -597,7 +598,8 @@ int acro_b200_gram(const double *X, const double *Y, double *S, int64_t rows, in
         pa.k = pa.rows_a = pa.rows_b = tail;
         pa.wide = (aligned16(pa.A) && aligned16(pa.B) && a % 2 == 0 && b % 2 == 0) ? 1 : 0;
         kernel<<<1, NT, smem, st>>>(pa);
-        if (cudaGetLastError() != cudaSuccess) return launch_status("acro_b200_gram (last rows)");
+        const int launched = launch_status("acro_b200_gram (last rows)");
+        if (launched != ACRO_B200_OK) return launched;
         ++parts;
     }
     gram_combine_kernel<<<(entries + 255) / 256, 256, 0, st>>>(S, scratch, parts, entries, op);

@@ -24,6 +24,11 @@ int sm_count();
 // up (nullptr on failure); acro_b200_device_status() reads and clears it.
 int *wait_flag_device_ptr();
 
+// Number of acro_b200_set_context calls so far.  The address of a __device__ symbol belongs to one CUDA
+// context, so code that caches such an address stores this value with it and looks the address up
+// again when the value has moved on.
+unsigned long long context_epoch();
+
 inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
 
 // To be called right after a kernel launch.

@@ -17,12 +17,13 @@ struct acro_b200_peer_group
 
 namespace acro_b200_detail
 {
-PeerView next_peer_view(acro_b200_peer_group *g)
+PeerView next_peer_view(acro_b200_peer_group *g, int64_t exchanges)
 {
     PeerView v;
     v.world = g->world;
     v.rank = g->rank;
-    v.seq = ++g->seq;
+    v.seq = g->seq + 1;
+    g->seq += static_cast<unsigned long long>(exchanges < 1 ? 1 : exchanges);
     for (int p = 0; p < ACRO_B200_MAX_PEERS; ++p)
     {
         char *base = static_cast<char *>(p < g->world ? g->peer[p] : nullptr);
@@ -33,7 +34,84 @@ PeerView next_peer_view(acro_b200_peer_group *g)
 }
 }
 
+namespace
+{
+
+constexpr int kAllreduceThreads = 1024;
+
+// dst[i] (op)= sum over the ranks of src[i], i < n.  One CTA walks the entries in exchanges of at most
+// kPeerSlot: it stores its own values into every rank's mailbox (plain remote stores), publishes the
+// exchange's sequence number, waits (bounded, polling its own memory) for the other ranks and adds
+// the world contributions in rank order, so every rank ends with the same bits.  src == dst is allowed
+// (each entry is read and written by the same thread).  When a wait gives up the flag is raised and
+// the remaining exchanges are skipped: the result is invalid and nothing hangs.
+__global__ void __launch_bounds__(kAllreduceThreads)
+peer_allreduce_kernel(double *dst, const double *src, int64_t n, int op, PeerView pv, int *wait_flag)
+{
+    __shared__ int gave_up;
+    const int t = threadIdx.x;
+    if (t == 0) gave_up = 0;
+    __syncthreads();
+    for (int64_t base = 0; base < n; base += kPeerSlot, ++pv.seq)
+    {
+        const int len = static_cast<int>(n - base < kPeerSlot ? n - base : kPeerSlot);
+        const int par = static_cast<int>(pv.seq & 1ull);
+        const size_t slot = (static_cast<size_t>(par) * pv.world + pv.rank) * kPeerSlot;
+        for (int i = t; i < len; i += kAllreduceThreads)
+        {
+            const double v = src[base + i];
+            for (int p = 0; p < pv.world; ++p) pv.data[p][slot + i] = v;
+        }
+        __threadfence_system();     // also orders the previous exchange's mailbox reads before this publication
+        __syncthreads();
+        if (t < pv.world)
+        {
+            volatile unsigned long long *remote = pv.flag[t] + static_cast<size_t>(par) * pv.world + pv.rank;
+            *remote = pv.seq;
+            volatile unsigned long long *own = pv.flag[pv.rank] + static_cast<size_t>(par) * pv.world + t;
+            bool arrived = false;
+            for (unsigned int tries = 0; tries < (1u << 21); ++tries)   // about a second
+            {
+                if (*own >= pv.seq) { arrived = true; break; }
+                __nanosleep(64);
+            }
+            if (!arrived)
+            {
+                atomicExch(wait_flag, 1);
+                gave_up = 1;
+            }
+            __threadfence_system();
+        }
+        __syncthreads();
+        if (gave_up != 0) return;
+        const volatile double *box = pv.data[pv.rank] + static_cast<size_t>(par) * pv.world * kPeerSlot;
+        for (int i = t; i < len; i += kAllreduceThreads)
+        {
+            double total = 0.0;
+            for (int r = 0; r < pv.world; ++r) total += box[static_cast<size_t>(r) * kPeerSlot + i];
+            if (op == ACRO_B200_OP_ASSIGN) dst[base + i] = total;
+            else if (op == ACRO_B200_OP_ADD) dst[base + i] += total;
+            else dst[base + i] -= total;
+        }
+    }
+}
+
+}
+
 extern "C" {
+
+int acro_b200_peer_allreduce(double *dst, const double *src, int64_t n, int op, acro_b200_peer_group *group, void *stream)
+{
+    if (dst == nullptr || src == nullptr || group == nullptr) return fail_invalid("acro_b200_peer_allreduce: null argument");
+    if (n < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_peer_allreduce: bad count or operator");
+    if (!group->connected) return fail_invalid("acro_b200_peer_allreduce: the peer group is not connected");
+    int *wait_flag = wait_flag_device_ptr();
+    if (wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_peer_allreduce (status flag)");
+    const int64_t exchanges = (n + kPeerSlot - 1) / kPeerSlot;
+    const PeerView pv = next_peer_view(group, exchanges);
+    peer_allreduce_kernel<<<1, kAllreduceThreads, 0, as_stream(stream)>>>(dst, src, n, op, pv, wait_flag);
+    return launch_status("acro_b200_peer_allreduce");
+}
 
 int acro_b200_peer_group_create(int world, int rank, acro_b200_peer_group **out, unsigned char *handle_out)
 {

@@ -53,7 +53,7 @@ struct ReduceArgs
 __device__ __forceinline__ double exchange_with_peers(const PeerView &pv, int t, int F, double mine, int *wait_flag)
 {
     const int par = static_cast<int>(pv.seq & 1ull);
-    const size_t slot = (static_cast<size_t>(par) * pv.world + pv.rank) * kPeerMaxF;
+    const size_t slot = (static_cast<size_t>(par) * pv.world + pv.rank) * kPeerSlot;
     if (t < F)
     {
         for (int p = 0; p < pv.world; ++p) pv.data[p][slot + t] = mine;   // remote stores over the peer mapping
@@ -80,8 +80,8 @@ __device__ __forceinline__ double exchange_with_peers(const PeerView &pv, int t,
     double total = 0.0;
     if (t < F)
     {
-        const volatile double *box = pv.data[pv.rank] + static_cast<size_t>(par) * pv.world * kPeerMaxF;
-        for (int r = 0; r < pv.world; ++r) total += box[static_cast<size_t>(r) * kPeerMaxF + t];
+        const volatile double *box = pv.data[pv.rank] + static_cast<size_t>(par) * pv.world * kPeerSlot;
+        for (int r = 0; r < pv.world; ++r) total += box[static_cast<size_t>(r) * kPeerSlot + t];
     }
     return total;
 }
@@ -228,6 +228,10 @@ static int launch_reduce(const double *A, const double *w, double *out, int64_t 
                          size_t scratch_bytes, acro_b200_peer_group *group, void *stream)
 {
     if (A == nullptr || out == nullptr || scratch == nullptr) return fail_invalid("acro_b200_reduce_batch: null argument");
+    // The ticket counter must be zero when the kernel starts, and the kernel leaves it zero.  A caller
+    // that zeroed it once may say so and save the clear in front of every launch.
+    const bool counter_is_zero = (op & ACRO_B200_SCRATCH_READY) != 0;
+    op &= ~ACRO_B200_SCRATCH_READY;
     if (rows < 1 || op < 0 || op > 2) return fail_invalid("acro_b200_reduce_batch: bad rows or operator");
     if (F < 1 || F > kMaxThreads / 2) return fail_unsupported("acro_b200_reduce_batch: row length must be 1..256");
     if (scratch_bytes < acro_b200_reduce_batch_scratch_bytes(F)) return fail_invalid("acro_b200_reduce_batch: scratch buffer too small");
@@ -258,15 +262,18 @@ static int launch_reduce(const double *A, const double *w, double *out, int64_t 
     if (group != nullptr)
     {
         if (acro_b200_peer_group_is_connected(group) != 1) return fail_invalid("acro_b200_reduce_batch_allreduce: the peer group is not connected");
-        if (F > kPeerMaxF) return fail_unsupported("acro_b200_reduce_batch_allreduce: row length exceeds the mailbox slot");
+        if (F > kPeerSlot) return fail_unsupported("acro_b200_reduce_batch_allreduce: row length exceeds the mailbox slot");
         args.wait_flag = wait_flag_device_ptr();
         if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_reduce_batch_allreduce (status flag)");
         pv = next_peer_view(group);
     }
 
     cudaStream_t s = as_stream(stream);
-    cudaError_t status = cudaMemsetAsync(args.counter, 0, kCounterBytes, s);
-    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_reduce_batch (counter reset)");
+    if (!counter_is_zero)
+    {
+        cudaError_t status = cudaMemsetAsync(args.counter, 0, kCounterBytes, s);
+        if (status != cudaSuccess) return fail_cuda(status, "acro_b200_reduce_batch (counter reset)");
+    }
     const size_t smem = 2 * static_cast<size_t>(T) * sizeof(double);
     const bool vec = aligned16(A);
     const int g = static_cast<int>(grid);
@@ -326,7 +333,8 @@ int acro_b200_reduce_batch_noalloc_max_f(void) { return kNoAllocMaxF; }
 // device address, so the address is looked up with cudaGetSymbolAddress, once per device
 // and with that device current, the first time this function runs on the device.  That
 // first call should therefore happen before any stream capture begins.  Later calls only
-// read the cached address.
+// read the cached address.  A call of acro_b200_set_context makes the next call on every
+// device a first call again (the address is per context), with the same rule about capture.
 //
 // The function itself calls no cudaMalloc / cudaFree and no allocating library routine.
 // All calls on one GPU share the one scratch array, which still holds the previous call's
@@ -344,6 +352,7 @@ int acro_b200_reduce_batch_noalloc(const double *A, const double *w, double *out
     constexpr int kMaxDevices = 64;
     static std::mutex lock;
     static double *scratch_of_device[kMaxDevices] = {nullptr};
+    static unsigned long long epoch_of_device[kMaxDevices] = {0};
     int dev = -1;
     cudaError_t status = cudaGetDevice(&dev);
     if (status != cudaSuccess) return fail_cuda(status, "acro_b200_reduce_batch_noalloc (cudaGetDevice)");
@@ -351,12 +360,16 @@ int acro_b200_reduce_batch_noalloc(const double *A, const double *w, double *out
     double *scratch = nullptr;
     {
         std::lock_guard<std::mutex> guard(lock);
-        if (scratch_of_device[dev] == nullptr)
+        // The symbol has one address per CUDA context: after acro_b200_set_context the address
+        // found earlier belongs to the context that was current then, so it is looked up again.
+        const unsigned long long epoch = context_epoch();
+        if (scratch_of_device[dev] == nullptr || epoch_of_device[dev] != epoch)
         {
             void *ptr = nullptr;
             status = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
             if (status != cudaSuccess) return fail_cuda(status, "acro_b200_reduce_batch_noalloc (cudaGetSymbolAddress)");
             scratch_of_device[dev] = static_cast<double *>(ptr);
+            epoch_of_device[dev] = epoch;
         }
         scratch = scratch_of_device[dev];
     }

@@ -159,6 +159,35 @@ class Tensor:
     def SetTransient(self, flag=True):
         check(lib().acro_tensor_set_transient(self._h, int(bool(flag))))
 
+    def SetSharded(self, flag=True):
+        """This tensor is this rank's slab of a tensor cut along its leading dimension over the ranks
+        of a peer group (see TensorEngine.SetPeerGroup)."""
+        check(lib().acro_tensor_set_sharded(self._h, int(bool(flag))))
+
+    def IsSharded(self):
+        return bool(lib().acro_tensor_is_sharded(self._h))
+
+
+def batch_slab(batch, rank, world):
+    """acro::SlabOf: the contiguous range [begin, end) of a batch index of extent `batch` owned by
+    `rank` of `world` (host arithmetic of the library; no device needed)."""
+    b, e = ctypes.c_int64(), ctypes.c_int64()
+    check(lib().acro_b200_batch_slab(int(batch), int(rank), int(world), ctypes.byref(b), ctypes.byref(e)))
+    return b.value, e.value
+
+
+class SlabTensor(Tensor):
+    """acro::SlabTensor(T, begin, end) / SlabTensor(T, rank=, world=): rows [begin, end) of the leading
+    dimension of T, sharing T's host buffer, with a device mirror of the slab only; flagged sharded."""
+
+    def __init__(self, parent, begin=None, end=None, rank=None, world=None):
+        if begin is None:
+            begin, end = batch_slab(parent.GetDim(0), rank, world)
+        h = ctypes.c_void_p()
+        check(lib().acro_tensor_slab(parent._h, int(begin), int(end), ctypes.byref(h)))
+        super().__init__(_handle=h, _keep=parent)
+        self.begin, self.end = int(begin), int(end)
+
 
 class SliceTensor(Tensor):
     """acro::SliceTensor(T, i0, ...): the trailing dimensions of T at a fixed prefix."""
@@ -370,8 +399,10 @@ class TensorEngine:
         return isCudaReady()
 
     def SetPeerGroup(self, group):
-        """Attach a PeerGroup (None detaches): contractions over a sharded, contracted batch index
-        then return the sum over all ranks (reduction and all-reduce fused in one kernel)."""
+        """Attach a PeerGroup (None detaches): a contraction that sums over the leading index of an
+        input flagged sharded (SlabTensor, Tensor.SetSharded) then returns the sum over all ranks'
+        slabs on every rank (inside the kernel for the reduce_batch family, by an all-reduce kernel
+        after the step for every other family)."""
         self._peer_group = group
         check(lib().acro_engine_set_peer_group(self._h, group._h if group is not None else None))
 

@@ -7,12 +7,12 @@ holds a partial result and one all-reduce(sum) of the small output finishes the 
 """
 import numpy as np
 
-from .host import Tensor, TensorEngine
+from .host import Tensor, TensorEngine, batch_slab
 
 
 def slab(batch, rank, world):
-    """Contiguous range [begin, end) of the batch index owned by `rank` of `world`."""
-    return batch * rank // world, batch * (rank + 1) // world
+    """Contiguous range [begin, end) of the batch index owned by `rank` of `world` (acro::SlabOf)."""
+    return batch_slab(batch, rank, world)
 
 
 class Session:
@@ -23,9 +23,11 @@ class Session:
     device: name -> torch CUDA float64 tensor used as the externally owned device mirror
             (optional; without it MapToGPU allocates).
     transient: flag chain intermediates as transient so a fused plan may keep them on chip.
+    sharded: the batched tensors are this rank's slabs of the batch index (Tensor.SetSharded): with a
+            peer group attached to the engine a contraction over the batch index is summed over ranks.
     """
 
-    def __init__(self, workload, host, device=None, transient=True, engine=None):
+    def __init__(self, workload, host, device=None, transient=True, engine=None, sharded=False):
         self.w = workload
         self.host = host
         self.device = device or {}
@@ -35,6 +37,8 @@ class Session:
             self.t[name] = Tensor(host[name].shape, hdata=host[name], ddata=self.device.get(name))
             if transient and workload.tensors[name][2] == "tmp":
                 self.t[name].SetTransient(True)
+            if sharded and workload.batched(name):
+                self.t[name].SetSharded(True)
 
     def to_device(self, names=None):
         for name in names or self.w.names("in"):

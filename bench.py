@@ -12,9 +12,9 @@ configuration.  `e2e` is the same metric through the public engine API with HOST
 (pinned), host->device and device->host copies inside the timed region.
 
 For N > 1 launch with torchrun (one rank per GPU).  The batch index is cut into per-rank
-slabs; "weak" (default) gives every rank a full-size slab, "strong" splits the full size.
-Only the README reduction (batch index contracted) needs a collective: one all-reduce of
-its 3x3 result per step, inside the timed region.
+slabs; "strong" (default) cuts the benchmark sizes into N slabs, "weak" gives every rank a
+full-size slab.  Only the README reduction (batch index contracted) needs a collective: one
+all-reduce of its 3x3 result per step, inside the timed region.
 
 `--impl reference` times the reference's own CPU executor (the unmodified sources compiled
 into oracle/_ref, else the C restatement) on all host threads, on bounded samples.
@@ -34,12 +34,14 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 
 FALLBACK_HBM_GBS = 6650.0
-# fp64 peak of a B200 measured on this pool with a register-resident DFMA chain
-# (profiles/fp64_peak_microbenchmark.md); used for the compute-bound configurations.
+# fp64 peak of a B200: the tensor-core (DMMA) microbenchmark figure measured on this pool, read from
+# a one-number text file kept with the profile summaries; used for the compute-bound configurations.
 FP64_PEAK_GFLOPS_FILE = os.path.join(ROOT, "profiles", "fp64_peak_gflops.txt")
-# dram bytes (read+write) per launch of the dominant kernel from the ncu capture summarised
-# in profiles/ (scaled to a full-size launch); None until captured.
-NCU_TRAFFIC_BYTES = {"cfg3": 9.79e9, "cfg0": 5.40e9, "cfg2": 2.01e9, "cfg1": 1.42e9, "cfg4": 1.36e9}   # profiles/*_ncu.md, small captures scaled to a full launch
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE benchmark-size launch of each
+# configuration's kernel, from ncu captures of smaller launches scaled in proportion to the batch
+# (traffic of these streaming kernels grows linearly with it).  Measured once per kernel version by
+# hand: these numbers do not follow a code change by themselves.
+NCU_TRAFFIC_BYTES = {"cfg3": 9.79e9, "cfg0": 5.40e9, "cfg2": 2.01e9, "cfg1": 1.42e9, "cfg4": 1.36e9}
 
 # batch of the bounded CPU sample per configuration (about 1-2 s of one core each)
 CPU_SAMPLE = {"cfg0": 1 << 24, "cfg1": 1 << 12, "cfg2": 1 << 16, "cfg3": 1 << 16, "cfg4": 1 << 9}
@@ -142,6 +144,12 @@ def host_memory_available():
     return avail
 
 
+def launch_traffic(w, batch):
+    """ncu DRAM bytes of one launch over `batch` units, scaled from the benchmark-size figure."""
+    full = NCU_TRAFFIC_BYTES.get(w.key)
+    return None if full is None else round(full * batch / w.batch)
+
+
 def selected(workload):
     from acrotensor_b200.workloads import BY_KEY, WORKLOADS
     return list(WORKLOADS) if workload == "suite" else [BY_KEY[workload]]
@@ -236,11 +244,14 @@ def run_ours(args):
             # untouched pageable placeholder; the end-to-end leg retargets tensors to pinned buffers
             host[name] = torch.empty(shape, dtype=torch.float64).numpy()
         torch.cuda.synchronize()
-        sess = Session(w, host, device=dict(dev_t), transient=True)
-        if w.batch_contracted and world > 1 and args.allreduce == "fused":
+        # N > 1: every batched tensor is this rank's slab of the batch index and is flagged as such; the engine
+        # sums a result over the ranks of its peer group only where a string contracts that index (cfg0: reduction
+        # and all-reduce in one kernel, over NVLink peer memory) and leaves every other configuration alone
+        sess = Session(w, host, device=dict(dev_t), transient=True, sharded=world > 1)
+        if world > 1 and args.allreduce == "fused":
             if peer_group is None:
                 peer_group = make_peer_group()
-            sess.te.SetPeerGroup(peer_group)     # reduction and all-reduce in one kernel, over NVLink peer memory
+            sess.te.SetPeerGroup(peer_group)
         sess.keep = dev_t
         sessions.append(sess)
         outs_dev.append({n: dev_t[n] for n in w.names("out")})
@@ -303,8 +314,18 @@ def run_ours(args):
     per_cfg_ms = [float(np.median([ev[k][i][0].elapsed_time(ev[k][i][1]) for k in range(args.steps)]))
                   for i in range(len(workloads))]
 
-    # parity spot check of what was just computed (sampled units, untimed)
+    # parity spot check of what was just computed (sampled units, untimed); the contracted configuration and
+    # the rank-sum of a Gram string are checked by all ranks together
     parity = spot_check(workloads, sessions, batches, world) if rank == 0 else None
+    across = contracted_parity(workloads, sessions, batches, world, rank, dev)
+    if world > 1 and peer_group is not None:
+        across["gram_rank_sum"] = gram_rank_sum_check(peer_group, world, rank, dev)
+    if rank == 0:
+        parity.update(across)
+        if world == 1 and args.scale >= 1 and not args.no_cpu_baseline:
+            full = cfg0_against_reference(workloads, sessions, batches)
+            if full is not None:
+                parity["cfg0_vs_reference_full"] = full
 
     # end to end: host buffers, copies inside the timed region
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
@@ -403,11 +424,15 @@ def run_ours(args):
         for w, g, ms, b in zip(workloads, glob, per_cfg_ms, batches):
             gbs = w.bytes(g) / ms * 1e-6
             gfl = w.flops(g) / ms * 1e-6
+            frac_hbm = gbs / (hbm_peak * world)
+            frac_fp64 = w.executed_flops_fn(g) / ms * 1e-6 / (fp64_peak * world)
             per_config[w.key] = {
                 "batch": g, "ms": round(ms, 4), "GBps": round(gbs, 1), "GFLOPps": round(gfl, 1),
-                "bound": w.bound, "frac_hbm": round(gbs / (hbm_peak * world), 4),
-                "frac_fp64": round(gfl / (fp64_peak * world), 4),
-                "frac_fp64_executed": round(w.executed_flops_fn(g) / ms * 1e-6 / (fp64_peak * world), 4)}
+                "bound": w.bound, "frac": round(frac_hbm if w.bound == "hbm" else frac_fp64, 4),
+                "frac_hbm": round(frac_hbm, 4),
+                # flops the kernel executes (cfg1 computes only the 378 + 6 packed columns of its symmetric result)
+                "frac_fp64_executed": round(frac_fp64, 4),
+                "algorithmic_GFLOPps_over_fp64_peak": round(gfl / (fp64_peak * world), 4)}
         # the dominant kernel: the one with the largest share of the step
         dom = int(np.argmax(per_cfg_ms))
         wd = workloads[dom]
@@ -415,21 +440,24 @@ def run_ours(args):
         if wd.bound == "hbm":
             achieved = dom_bytes / per_cfg_ms[dom] * 1e-6
             roof = {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
-                    "frac": round(achieved / hbm_peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(wd.key),
+                    "frac": round(achieved / hbm_peak, 4), "traffic": launch_traffic(wd, batches[dom]),
                     "kernel": wd.key, "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback",
                     "algorithmic_bytes_per_launch": dom_bytes}
         else:
-            achieved = wd.flops(batches[dom]) / per_cfg_ms[dom] * 1e-9
+            achieved = wd.executed_flops_fn(batches[dom]) / per_cfg_ms[dom] * 1e-9
             roof = {"bound": "tensor", "achieved": round(achieved, 2), "peak": round(fp64_peak * 1e-3, 2), "unit": "TFLOP/s",
-                    "frac": round(achieved / (fp64_peak * 1e-3), 4), "traffic": NCU_TRAFFIC_BYTES.get(wd.key),
-                    "kernel": wd.key, "peak_source": "fp64 DFMA microbenchmark on this pool (not in MEASURED_PEAKS.json)",
-                    "algorithmic_flops_per_launch": wd.flops(batches[dom])}
+                    "frac": round(achieved / (fp64_peak * 1e-3), 4), "traffic": launch_traffic(wd, batches[dom]),
+                    "kernel": wd.key, "peak_source": "fp64 tensor-core microbenchmark on this pool (not in MEASURED_PEAKS.json)",
+                    "executed_flops_per_launch": wd.executed_flops_fn(batches[dom])}
         line = {
             "metric": "contraction_throughput", "value": round(total_bytes / ms_per_step * 1e-6, 1), "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
             "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f64",
             "data": "synthetic (seeded, shapes and distributions of the benchmark configurations)",
-            "config": {"workload": args.workload + (": cfg0..cfg4 back to back" if args.workload == "suite" else ""),
+            "config": {"workload": args.workload + (": cfg0..cfg4 back to back" if args.workload == "suite" else "")
+                                   + (", benchmark sizes" if world == 1 else
+                                      (", benchmark sizes cut into %d slabs (strong scaling)" % world if args.scaling == "strong"
+                                       else ", a benchmark-size slab on each of %d ranks (weak scaling)" % world)),
                        "batches_per_gpu": {w.key: b for w, b in zip(workloads, batches)},
                        "l2": "inputs_exceed_l2 (every configuration streams >= 1.6 GB per GPU)" if args.scale >= 1 else "scaled-down run",
                        "parallelism": "batch slabs x%d, all-reduce only for the contracted batch index (%s)"
@@ -458,6 +486,103 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def contracted_parity(workloads, sessions, batches, world, rank, dev):
+    """The configuration whose batch index is contracted, at any N (collective: every rank calls it).  Each rank sums
+    its own slab with torch's fp64 tree reduction; the rank-ordered total of those sums is compared with the result
+    the engine left on this rank, and all ranks must hold the same bits."""
+    import torch
+    import torch.distributed as dist
+    found = {}
+    for w, sess, b in zip(workloads, sessions, batches):
+        if not w.batch_contracted:
+            continue
+        out = w.names("out")[0]
+        got = sess.keep[out].reshape(-1).clone()
+        mine = (sess.keep["A"].view(b, -1) * sess.keep["B"].view(b, 1)).sum(dim=0)
+        if world > 1:
+            sums = [torch.empty_like(mine) for _ in range(world)]
+            results = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(sums, mine)
+            dist.all_gather(results, got)
+        else:
+            sums, results = [mine], [got]
+        total = torch.zeros_like(mine)
+        for part in sums:          # rank order, as the exchange adds them
+            total += part
+        found[w.key] = float(((got - total).abs() / total.abs()).max().item())
+        found[w.key + "_same_bits_on_every_rank"] = bool(all(torch.equal(r, results[0]) for r in results))
+        found[w.key + "_ranks"] = world
+    return found
+
+
+def gram_rank_sum_check(peer_group, world, rank, dev):
+    """N > 1, untimed: a Gram string over a sharded row index, run through the engine on every rank (its own
+    family, followed by the all-reduce kernel), against the rank-ordered total of per-rank torch products."""
+    import torch
+    import torch.distributed as dist
+    import acrotensor_b200 as ab
+    rows, a = 1 << 16, 27
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4242 + rank)
+    x = torch.rand((rows, a), generator=gen, device=dev, dtype=torch.float64) - 0.5
+    y = torch.rand((rows, a), generator=gen, device=dev, dtype=torch.float64) - 0.5
+    s = torch.zeros((a, a), device=dev, dtype=torch.float64)
+    host = lambda t: torch.empty(tuple(t.shape), dtype=torch.float64).numpy()
+    X, Y, S = (ab.Tensor(tuple(t.shape), hdata=host(t), ddata=t, ongpu=True) for t in (x, y, s))
+    X.SetSharded(True)
+    Y.SetSharded(True)
+    te = ab.TensorEngine("Cuda")
+    te.SetPeerGroup(peer_group)
+    dist.barrier()
+    te("S_a_b = X_n_a Y_n_b", S, X, Y)
+    torch.cuda.synchronize()
+    parts = [torch.empty_like(s) for _ in range(world)]
+    mags = [torch.empty_like(s) for _ in range(world)]
+    results = [torch.empty_like(s) for _ in range(world)]
+    dist.all_gather(parts, x.t() @ y)
+    dist.all_gather(mags, x.abs().t() @ y.abs())
+    dist.all_gather(results, s)
+    total, scale = torch.zeros_like(s), torch.zeros_like(s)
+    for p_, m_ in zip(parts, mags):
+        total += p_
+        scale += m_
+    family = te.GetImplementation("S_a_b = X_n_a Y_n_b", S, X, Y).split("family=")[1].split()[0]
+    return {"string": "S_a_b = X_n_a Y_n_b", "rows_per_rank": rows, "family": family,
+            "max_err_over_sum_abs_terms": float(((s - total).abs() / scale).max().item()),
+            "same_bits_on_every_rank": bool(all(torch.equal(r, results[0]) for r in results))}
+
+
+def cfg0_against_reference(workloads, sessions, batches):
+    """N = 1, full size: the README reduction over all 2^26 rows that the GPU just summed, recomputed from the SAME
+    inputs (downloaded from the device) by the reference CPU executor exactly as shipped (one thread, its own
+    summation order) and by a long-double sum; reports the relative deviations, it gates nothing."""
+    from oracle import oracle
+    for w, sess, b in zip(workloads, sessions, batches):
+        if not w.batch_contracted:
+            continue
+        t0 = time.perf_counter()
+        a, wts = sess.keep["A"].cpu().numpy(), sess.keep["B"].cpu().numpy()
+        got = sess.keep[w.names("out")[0]].cpu().numpy()
+        ref = np.zeros_like(got)
+        kind = "reference" if oracle.have("ref") else "port"
+        if kind == "reference":
+            oracle.run_ref_slabs([ref, a, wts], [(w.program[0][0], 0, [1, 2])], [False, True, True], b, 1)
+        else:
+            oracle.contract("port", w.program[0][0], ref, a, wts)
+        exact = np.zeros(got.size, dtype=np.longdouble)
+        flat = a.reshape(b, -1)
+        for r0 in range(0, b, 1 << 22):
+            r1 = min(b, r0 + (1 << 22))
+            exact += (flat[r0:r1] * wts[r0:r1, None]).sum(axis=0, dtype=np.longdouble)
+        exact = exact.reshape(got.shape)
+        rel = lambda x, y: float(np.max(np.abs((x.astype(np.longdouble) - y) / y)))
+        return {"rows": b, "checker": kind + " CPU executor, one thread, on the inputs downloaded from the device",
+                "gpu_vs_reference_executor": float(np.max(np.abs(got - ref) / np.abs(ref))),
+                "gpu_vs_long_double_sum": rel(got, exact), "reference_executor_vs_long_double_sum": rel(ref, exact),
+                "seconds": round(time.perf_counter() - t0, 1)}
+    return None
+
+
 def spot_check(workloads, sessions, batches, world):
     """Compares a few batch units of every result with the C restatement (untimed)."""
     import torch
@@ -465,15 +590,7 @@ def spot_check(workloads, sessions, batches, world):
     worst = {}
     for w, sess, b in zip(workloads, sessions, batches):
         if w.batch_contracted:
-            if world > 1:
-                continue      # the all-reduced value mixes every rank's data
-            out = w.names("out")[0]
-            got = sess.keep[out].cpu().numpy()
-            # column sums recomputed on the device data with torch's fp64 tree reduction
-            a = sess.keep["A"]
-            ref = (a.view(b, -1).to(torch.float64) * sess.keep["B"].view(b, 1)).sum(dim=0).cpu().numpy().reshape(got.shape)
-            worst[w.key] = float(np.max(np.abs(got - ref) / np.abs(ref)))
-            continue
+            continue          # checked by contracted_parity (every rank takes part)
         take = sorted(set([0, b // 2, b - 1]))
         tensors = {}
         for name in w.tensors:
@@ -487,7 +604,8 @@ def spot_check(workloads, sessions, batches, world):
         oracle.run("port", mags, prog, multi=w.multi)
         worst[w.key] = max(oracle.parity_error(got[n], tensors[n], mags[names.index(n)]) for n in w.names("out"))
     return {"max_err_over_sum_abs_terms": worst, "tolerance": 1e-12,
-            "note": "cfg0 vs a device-side fp64 tree sum (relative); others vs the oracle on sampled units"}
+            "note": "sampled batch units of this rank's slab against the oracle; cfg0 (and, for N > 1, the rank sum of a "
+                    "Gram string) against the rank-ordered total of every rank's device-side fp64 sum"}
 
 
 def run_ops(args):
@@ -755,7 +873,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="suite", choices=["suite", "cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "ops"])
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
+                    help="N > 1: strong = the benchmark sizes cut into N slabs (default), weak = a full-size slab per rank")
     ap.add_argument("--scale", type=float, default=1.0, help="multiplies every batch size (debugging; 1.0 = benchmark sizes)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--e2e-steps", type=int, default=3)

@@ -4,6 +4,7 @@
 #include "TensorEngine.hpp"
 #include "Executor.hpp"
 #include "SliceTensor.hpp"
+#include "SlabTensor.hpp"
 #include "IndexMapping.hpp"
 #include "SharedEntryExchange.hpp"
 #endif

@@ -12,6 +12,9 @@
 //   generic          any other string: one thread per output entry, terms summed in the
 //                    reference CPU executor's order (bit-identical results for "=")
 // There is no CPU fallback: a shape no family covers runs on the generic GPU kernel.
+// Multi-GPU (one process per GPU): with a peer group attached, a step that contracts the leading
+// index of an input flagged Tensor::IsSharded() is completed by the sum over the ranks, inside the
+// kernel for reduce_batch and by the all-reduce kernel acro_b200_peer_allreduce for every other family.
 #ifndef ACRO_B200_EXECUTOR_HPP
 #define ACRO_B200_EXECUTOR_HPP
 
@@ -39,8 +42,12 @@ class B200Executor : public KernelExecutor
     void Run(std::vector<Tensor *> &outputs, std::vector<std::vector<Tensor *>> &inputs);
     std::unique_ptr<plan::Program> Fused;      // plan that may elide transient intermediates
     std::unique_ptr<plan::Program> Unfused;    // plan that materialises every output
-    double *Scratch;
+    double *Scratch;            // work space of the step that is running (shared by the families)
     std::size_t ScratchBytes;
+    double *ReduceScratch;      // ticket counter and CTA partial sums of reduce_batch, kept zeroed between launches
+    std::size_t ReduceScratchBytes;
+    double *RankSum;            // this rank's partial result of a "+=" / "-=" contraction that is summed over ranks
+    std::size_t RankSumBytes;
 };
 
 }

@@ -10,7 +10,9 @@
 //     benchmark configurations overflow a 32-bit byte count);
 //   * device memory this object allocated is always released by it;
 //   * SetTransient() lets a tensor that only links two kernels of a
-//     multi-kernel launch stay on chip (see TensorEngine).
+//     multi-kernel launch stay on chip (see TensorEngine);
+//   * SetSharded() says that this tensor is one rank's slab of a larger tensor
+//     cut along its leading dimension (see SlabTensor and TensorEngine::SetPeerGroup).
 #ifndef ACRO_B200_TENSOR_HPP
 #define ACRO_B200_TENSOR_HPP
 
@@ -155,6 +157,12 @@ class Tensor
     void SetTransient(bool transient) { Transient = transient; }
     bool IsTransient() const { return Transient; }
 
+    // Multi-GPU, one process per GPU: this tensor holds this rank's slab of a tensor whose leading
+    // (slowest) dimension is cut over the ranks of the engine's peer group.  A contraction that sums
+    // over that dimension then returns the sum over every rank's slab (TensorEngine::SetPeerGroup).
+    void SetSharded(bool sharded) { Sharded = sharded; }
+    bool IsSharded() const { return Sharded; }
+
     protected:
     void UpdateStrides();
 
@@ -168,6 +176,7 @@ class Tensor
     bool MappedToGPU;
     bool OnGPU;
     bool Transient;
+    bool Sharded;
     double *Data;
     double *DeviceData;
 };

@@ -48,6 +48,10 @@ extern "C" {
 #define ACRO_B200_OP_ASSIGN 0 /* "="  */
 #define ACRO_B200_OP_ADD 1    /* "+=" */
 #define ACRO_B200_OP_SUB 2    /* "-=" */
+/* May be or-ed into the `op` of the reduce_batch entry points that take caller-provided scratch: the
+ * caller zeroed the first 256 bytes of that scratch buffer once (cudaMemset) and nothing but
+ * reduce_batch calls has written to it since, so the clear in front of every launch is skipped. */
+#define ACRO_B200_SCRATCH_READY 0x100
 
 const char *acro_b200_last_error(void);
 
@@ -168,6 +172,14 @@ int acro_b200_peer_group_is_connected(const acro_b200_peer_group *group);
 int acro_b200_reduce_batch_allreduce(const double *A, const double *w, double *out, int64_t rows, int F, int op,
                                      double *scratch, size_t scratch_bytes, acro_b200_peer_group *group,
                                      void *stream);
+/* The all-reduce on its own, for results any other kernel family left on each rank:
+ * dst[i] (op)= sum over the ranks of src[i], i < n (src == dst allowed).  One small kernel; the entries
+ * travel through the mailboxes in exchanges of at most 4096, summed in rank order (bit-identical on
+ * every rank).  Every wait is bounded (about a second): an absent rank shows as ACRO_B200_ETIMEOUT in
+ * acro_b200_device_status() and the result is then invalid.  All ranks must make the same sequence of
+ * calls, with the same n, on this group. */
+int acro_b200_peer_allreduce(double *dst, const double *src, int64_t n, int op, acro_b200_peer_group *group,
+                             void *stream);
 
 /*
  * reduce_batch without any allocation.  No counterpart in the reference.
@@ -182,7 +194,9 @@ int acro_b200_reduce_batch_allreduce(const double *A, const double *w, double *o
  *   - rows of at most acro_b200_reduce_batch_noalloc_max_f() = 32 entries, otherwise
  *     ACRO_B200_EUNSUPPORTED (use acro_b200_reduce_batch with your own scratch);
  *   - the first call on each device looks up the array's device address (a one-time
- *     set-up, done with that device current); make that call before any stream capture;
+ *     set-up, done with that device current); make that call before any stream capture.
+ *     The address belongs to the CUDA context that was current then: after
+ *     acro_b200_set_context the next call on each device is a first call again;
  *   - every call on a GPU shares the one array, so calls that overlap on that GPU race:
  *     keep them on one stream or order them yourself.
  * Results are identical to acro_b200_reduce_batch's.
@@ -399,6 +413,18 @@ int acro_tensor_reshape(acro_tensor *t, int rank, const int *dims);
 int acro_tensor_retarget(acro_tensor *t, double *hdata, double *ddata);
 int acro_tensor_set_transient(acro_tensor *t, int transient);
 
+/* Multi-GPU, one process per GPU (no counterpart in the reference, which is single-device,
+ * exec/CudaExecutor.cpp:21).  acro_b200_batch_slab: the range [*begin, *end) of a batch index of
+ * extent `batch` that rank `rank` of `world` owns (contiguous, rank order, sizes differing by at most
+ * one; host arithmetic only, acro::SlabOf).  acro_tensor_slab: rows [begin, end) of the leading
+ * dimension of `parent` as a tensor that shares the parent's host buffer, owns a device mirror of the
+ * slab only and is flagged sharded (acro::SlabTensor; offset arithmetic as tensor/SliceTensor.cpp:142-168).
+ * acro_tensor_set_sharded: flags a tensor the caller built per rank as such a slab (Tensor::SetSharded). */
+int acro_b200_batch_slab(int64_t batch, int rank, int world, int64_t *begin, int64_t *end);
+int acro_tensor_slab(acro_tensor *parent, int64_t begin, int64_t end, acro_tensor **out);
+int acro_tensor_set_sharded(acro_tensor *t, int sharded);
+int acro_tensor_is_sharded(const acro_tensor *t);
+
 /* TensorEngine(exec_type), kernel/TensorEngine.cpp:27-48. */
 int acro_engine_create(const char *exec_type, acro_engine **out);
 int acro_engine_destroy(acro_engine *e);
@@ -416,9 +442,11 @@ int acro_engine_end_multi(acro_engine *e);
 /* Ends the recording and returns the description of the fused plan instead of running it. */
 int acro_engine_end_multi_describe(acro_engine *e, char *buf, size_t buf_len);
 int acro_engine_clear(acro_engine *e);
-/* Attach (or detach with NULL) a peer group: from then on a contraction whose contracted batch
- * index is planned as reduce_batch returns the sum over all ranks' slabs (fused all-reduce).
- * The engine does not own the group. */
+/* Attach (or detach with NULL) a peer group: from then on a contraction that sums over the leading
+ * index of an input flagged sharded (acro_tensor_slab, acro_tensor_set_sharded) returns, on every
+ * rank, the sum over all ranks' slabs: inside the kernel for the reduce_batch family, through
+ * acro_b200_peer_allreduce after the step for every other family.  Every rank of the group must
+ * make the same sequence of such calls.  The engine does not own the group. */
 int acro_engine_set_peer_group(acro_engine *e, acro_b200_peer_group *group);
 /* cudaStream_t as void*; applies to later launches of this engine. */
 int acro_engine_set_stream(acro_engine *e, void *stream);

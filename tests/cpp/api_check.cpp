@@ -75,6 +75,32 @@ static void host_checks()
     CHECK_THROWS(SliceTensor(T, 0, 0, 0));
     CHECK_THROWS(S1.Retarget(buf));
 
+    // batch slabs: the cut of a batch index over ranks, and the leading-range view
+    {
+        std::int64_t covered = 0;
+        for (int r = 0; r < 3; ++r)
+        {
+            const BatchSlab sl = SlabOf(10, r, 3);
+            CHECK(sl.begin == covered && sl.size() >= 3 && sl.size() <= 4);
+            covered = sl.end;
+        }
+        CHECK(covered == 10);
+        CHECK(SlabOf((std::int64_t(1) << 62) + 5, 7, 8).end == (std::int64_t(1) << 62) + 5);
+        CHECK_THROWS(SlabOf(10, 3, 3));
+        SlabTensor mid(T, 1, 2), mine(T, SlabOf(T.GetDim(0), 1, 2));
+        CHECK(mine.GetBegin() == 1 && mine.GetEnd() == 2 && mine.GetData() == mid.GetData());
+        CHECK(mid.GetRank() == 3 && mid.GetDim(0) == 1 && mid.GetDim(2) == 4 && mid.IsSharded() && !T.IsSharded());
+        CHECK(mid.GetData() == T.GetData() + 12 && mid.GetBegin() == 1 && mid.GetEnd() == 2);
+        mid(0, 0, 1) = 77.0;
+        CHECK(T(1, 0, 1) == 77.0);
+        T(1, 0, 1) = -1.0;
+        SlabTensor whole(T, 0, 2);
+        CHECK(whole.GetSize() == 24 && !whole.IsMappedToGPU());
+        CHECK_THROWS(SlabTensor(T, 1, 1));
+        CHECK_THROWS(SlabTensor(T, 0, 3));
+        CHECK_THROWS(mid.Retarget(buf));
+    }
+
     // parser: accept / reject, names, index bookkeeping
     CHECK_THROWS(TensorKernel("Blah"));
     CHECK_THROWS(TensorKernel("Blah="));
@@ -118,6 +144,7 @@ static void host_checks()
     Tensor bigA(1 << 20, 3, 3, buf), bigB(1 << 20, buf), s33(3, 3);   // shape-only: never dereferenced here
     plan = TE.GetImplementation("S_i_j = A_n_i_j B_n", s33, bigA, bigB);
     CHECK(plan.find("family=reduce_batch") != std::string::npos);
+    CHECK(plan.find("summed over the ranks of a peer group when one of these inputs is a rank's slab: A B") != std::string::npos);
     TE.BeginMultiKernelLaunch();
     CHECK_THROWS(TE.BeginMultiKernelLaunch());
     TE("A_i = B_i", o3, v3);     // recorded only

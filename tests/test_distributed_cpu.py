@@ -83,3 +83,40 @@ def test_slabs_partition_the_batch():
 def test_allreduce_is_a_no_op_without_a_process_group():
     t = torch.arange(9, dtype=torch.float64)
     assert torch.equal(allreduce_partial(t.clone()), t)
+
+
+def plan_worker(rank, world, port, rows_of_rank, out_dir):
+    import acrotensor_b200 as ab
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rows = rows_of_rank[rank]
+        facts = []
+        for kernel, shapes in (("S_i_j = A_n_i_j B_n", [(3, 3), (rows, 3, 3), (rows,)]),
+                               ("S_a_b = X_n_a Y_n_b", [(27, 27), (rows, 27), (rows, 27)]),
+                               ("C_e_i_j = A_e_i_k B_e_k_j", [(rows, 4, 4), (rows, 4, 4), (rows, 4, 4)])):
+            text = ab.describe_plan([kernel], [shapes])
+            family = text.split("family=")[1].split()[0]
+            joins = "summed over the ranks" in text
+            facts.append((kernel, family, joins))
+        everyone = [None] * world
+        dist.all_gather_object(everyone, facts)
+        if rank == 0:
+            import json
+            with open(os.path.join(out_dir, "plans.json"), "w") as f:
+                json.dump(everyone, f)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_with_unequal_slabs_agree_on_which_results_are_summed_over_ranks(tmp_path):
+    """A rank with a short slab plans another kernel family than its peers (here 100 rows against 300000), but whether
+    a result is summed over the ranks depends on the string alone, so every rank joins the same exchanges."""
+    import json
+    world = 2
+    mp.spawn(plan_worker, args=(world, free_port(), [100, 300000], str(tmp_path)), nprocs=world, join=True)
+    with open(os.path.join(str(tmp_path), "plans.json")) as f:
+        short, long_ = json.load(f)
+    assert [f[1] for f in short] == ["generic", "generic", "batched_gemm"]
+    assert [f[1] for f in long_] == ["reduce_batch", "gram", "batched_gemm"]
+    assert [f[2] for f in short] == [f[2] for f in long_] == [True, True, False]

@@ -306,3 +306,51 @@ def test_planner_routes_sizes_and_layouts_to_the_expected_variants():
     assert "family=generic" in step0("A_i_j=B_j_i", (4, 5), (5, 4))
     # a plain matrix product is an assembly string with the batch index i and a single invariant factor
     assert "family=invariant_gemm" in step0("C_i_j = A_i_k B_k_j", (512, 512), (512, 512), (512, 512))
+
+
+def test_batch_slabs_and_the_leading_range_view():
+    """acro::SlabOf / acro::SlabTensor through the C ABI: host arithmetic and host-buffer sharing, no device."""
+    for batch in (0, 1, 7, 8, 1000, (1 << 26) + 3, (1 << 62) + 5):
+        for world in (1, 2, 3, 8, 16):
+            edges = [ab.batch_slab(batch, r, world) for r in range(world)]
+            assert edges[0][0] == 0 and edges[-1][1] == batch
+            assert all(a[1] == b[0] for a, b in zip(edges, edges[1:]))
+            sizes = [e - b for b, e in edges]
+            assert min(sizes) >= 0 and max(sizes) - min(sizes) <= 1
+    with pytest.raises(ab.AcroError):
+        ab.batch_slab(10, 3, 3)
+    full = np.arange(7 * 3 * 2, dtype=np.float64).reshape(7, 3, 2)
+    T = ab.Tensor(full.shape, hdata=full)
+    parts = [ab.SlabTensor(T, rank=r, world=3) for r in range(3)]
+    assert [p.shape[0] for p in parts] == [2, 2, 3] and all(p.shape[1:] == (3, 2) for p in parts)
+    assert all(p.IsSharded() and not p.IsMappedToGPU() for p in parts) and not T.IsSharded()
+    assert np.array_equal(np.concatenate([p.numpy() for p in parts]), full)
+    parts[1].numpy()[0, 0, 0] = -5.0           # the view shares the parent's host rows
+    assert full[2, 0, 0] == -5.0
+    with pytest.raises(ab.AcroError):
+        ab.SlabTensor(T, 3, 3)
+    with pytest.raises(ab.AcroError):
+        ab.SlabTensor(T, 0, 8)
+    plain = ab.Tensor(4, 4)
+    assert not plain.IsSharded()
+    plain.SetSharded(True)
+    assert plain.IsSharded()
+
+
+def test_plan_names_the_inputs_whose_leading_index_is_contracted():
+    """The rank-sum rule is a property of the string, whatever family runs it: the plan text lists the inputs
+    that, as a rank's slab, leave a partial sum behind."""
+    marker = "summed over the ranks of a peer group when one of these inputs is a rank's slab:"
+
+    def rank_sum_line(kernel, *shapes):
+        text = ab.describe_plan([kernel], [list(shapes)])
+        lines = [l.strip() for l in text.splitlines() if marker in l]
+        return lines[0][len(marker):].strip() if lines else None
+
+    assert rank_sum_line("S_i_j = A_n_i_j B_n", (3, 3), (100000, 3, 3), (100000,)) == "A B (all-reduce fused into the kernel)"
+    assert rank_sum_line("S_i_j = A_n_i_j B_n", (3, 3), (100, 3, 3), (100,)) == "A B (all-reduce kernel after the step)"   # short slab: generic
+    assert rank_sum_line("S_a_b = X_n_a Y_n_b", (27, 27), (100000, 27), (100000, 27)) == "X Y (all-reduce kernel after the step)"
+    assert rank_sum_line("S_a = X_n_a Y_n_a", (5,), (100000, 5), (100000, 5)) == "X Y (all-reduce kernel after the step)"
+    # the batch index survives: nothing to sum, although q leads B
+    assert rank_sum_line("C_e_i_j = A_e_i_k B_e_k_j", (10, 8, 8), (10, 8, 8), (10, 8, 8)) is None
+    assert rank_sum_line("M_e_i_j = W_e_q B_q_i B_q_j", (100, 27, 27), (100, 64), (64, 27), (64, 27)).startswith("B B")
