@@ -105,9 +105,10 @@ reduce_batch_kernel(const ReduceArgs a, const PeerView pv)
     const int r0 = e0 / F, r1 = e1 / F;
     double acc0 = 0.0, acc1 = 0.0;
 
-    int64_t tile = blockIdx.x;
-    // Main loop: kUnroll independent tiles in flight per thread.
-    for (; tile + static_cast<int64_t>(kUnroll - 1) * gridDim.x < full_tiles; tile += static_cast<int64_t>(kUnroll) * gridDim.x)
+    // Main loop: kUnroll independent tiles in flight per thread.  The last, incomplete group takes the same
+    // path with the missing tiles read as zeros (adding them changes nothing), so that its loads are in
+    // flight together as well instead of one after the other.
+    for (int64_t tile = blockIdx.x; tile < full_tiles; tile += static_cast<int64_t>(kUnroll) * gridDim.x)
     {
         double2 v[kUnroll];
         double w0[kUnroll], w1[kUnroll];
@@ -115,14 +116,19 @@ reduce_batch_kernel(const ReduceArgs a, const PeerView pv)
         for (int u = 0; u < kUnroll; ++u)
         {
             const int64_t tl = tile + static_cast<int64_t>(u) * gridDim.x;
-            const double *src = a.A + tl * tile_doubles + e0;
-            if (VECTOR) v[u] = __ldcs(reinterpret_cast<const double2 *>(src));
-            else { v[u].x = __ldcs(src); v[u].y = __ldcs(src + 1); }
-            if (WEIGHTED)
+            v[u] = make_double2(0.0, 0.0);
+            w0[u] = w1[u] = 0.0;
+            if (tl < full_tiles)
             {
-                const int64_t row = tl * tile_rows;
-                w0[u] = __ldg(a.w + row + r0);
-                w1[u] = __ldg(a.w + row + r1);
+                const double *src = a.A + tl * tile_doubles + e0;
+                if (VECTOR) v[u] = __ldcs(reinterpret_cast<const double2 *>(src));
+                else { v[u].x = __ldcs(src); v[u].y = __ldcs(src + 1); }
+                if (WEIGHTED)
+                {
+                    const int64_t row = tl * tile_rows;
+                    w0[u] = __ldg(a.w + row + r0);
+                    w1[u] = __ldg(a.w + row + r1);
+                }
             }
         }
 #pragma unroll
@@ -131,20 +137,6 @@ reduce_batch_kernel(const ReduceArgs a, const PeerView pv)
             if (WEIGHTED) { acc0 = fma(v[u].x, w0[u], acc0); acc1 = fma(v[u].y, w1[u], acc1); }
             else { acc0 += v[u].x; acc1 += v[u].y; }
         }
-    }
-    for (; tile < full_tiles; tile += gridDim.x)
-    {
-        const double *src = a.A + tile * tile_doubles + e0;
-        double2 v;
-        if (VECTOR) v = __ldcs(reinterpret_cast<const double2 *>(src));
-        else { v.x = __ldcs(src); v.y = __ldcs(src + 1); }
-        if (WEIGHTED)
-        {
-            const int64_t row = tile * tile_rows;
-            acc0 = fma(v.x, __ldg(a.w + row + r0), acc0);
-            acc1 = fma(v.y, __ldg(a.w + row + r1), acc1);
-        }
-        else { acc0 += v.x; acc1 += v.y; }
     }
     // Ragged tail (fewer rows than a tile): handled by the CTA whose turn it would be.
     if (static_cast<int64_t>(blockIdx.x) == full_tiles % gridDim.x)

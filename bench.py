@@ -291,20 +291,26 @@ def run_ours(args):
 
     # A rank whose host stalls for about a second while its launch queue is empty (a shared machine) makes
     # its peers' bounded waits give up; such a measurement is void and is taken again, twice at most.
+    # The step time is taken over launches that follow each other with nothing in between (an event between two
+    # launches keeps the second from being brought onto the SMs while the first drains); the per-configuration
+    # times come from a second pass of the same steps with an event on either side of every configuration.
     for attempt in range(3):
         any_rank_gave_up()                       # clear what warm-up or an earlier attempt left
         sampler = ClockSampler(local_rank)
         sampler.start()
-        ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in workloads]
-              for _ in range(args.steps)]
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         t0.record()
         for k in range(args.steps):
-            device_step(ev[k])
+            device_step()
         t1.record()
         barrier()
         clocks = sampler.stop()
+        ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in workloads]
+              for _ in range(args.steps)]
+        for k in range(args.steps):
+            device_step(ev[k])
+        barrier()
         if not any_rank_gave_up():
             break
     else:
@@ -465,6 +471,8 @@ def run_ours(args):
                                          ("fused into the reduction kernel over NVLink peer memory" if args.allreduce == "fused" else "NCCL"))},
             "gflops": round(total_flops / ms_per_step * 1e-6, 1),
             "per_config": per_config,
+            "per_config_note": "ms of each configuration from a second pass with an event on either side of it (median over the "
+                               "steps); ms_per_step and value from the pass without events between the launches",
             "roofline": roof,
             "e2e": ({"value": round(total_bytes / e2e_ms * 1e-6, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                      "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 2), "steps": e2e_steps,
