@@ -22,7 +22,10 @@
 // Algorithmic HBM traffic per element: 8*64 (W) + 8*NI*NJ (M) bytes.
 #include "common.cuh"
 #include "dmma.cuh"
+
+#include <cstdlib>
 #include "tma.cuh"
+#include "tmem.cuh"
 
 using namespace acro_b200_detail;
 
@@ -402,6 +405,270 @@ rank1_gemm_sym_kernel(const Rank1Args a)
     if (tid == 0) bulk_wait_all<0>();   // shared memory must outlive the stores that read it
 }
 
+// ------------------------------------------------------------------ symmetric variant, right operand in tensor memory
+// The same packed-column scheme, with the formed right operand BB[q,(i,j)] = B[q,i]*B[q,j] kept on chip for
+// the whole launch instead of being formed again for every tile.  For 27 x 27 and 64 quadrature points it is
+// 64 x 384 doubles = 192 KB: more than the register file or shared memory can spare, but it fits the SM's
+// 256 KB of tensor memory, which registers reach through a path of their own (tmem.cuh).  Every thread parks
+// the 96 fragment entries it needs (16 k-steps x 6 column tiles) once and reads them back, twelve per pair of
+// k-steps, in front of the tensor-core instructions that consume them.  That removes the two shared-memory
+// loads and the multiply per fragment entry from the inner loop, whose shared-memory traffic was as large as
+// its tensor-pipe time (the old variant measured 58 % tensor-pipe activity with the shared-memory pipe at
+// 57 % and conflicts on top): what is left there is the W fragment.
+//
+// One CTA of 16 warps per SM, as two groups of 8 warps.  A group works like a CTA of the old variant (its own
+// stream of 16-element tiles, W double buffer, image and bulk store, synchronised by a named barrier), so one
+// group's scatter and store overlap the other's tensor-core loop; warp w of either group uses the same
+// columns, so both groups read the one copy of BB that group 0 wrote.
+constexpr int TM_GROUPS = 2, TM_GROUP_WARPS = 8, TM_GROUP_THREADS = TM_GROUP_WARPS * 32, TM_THREADS = TM_GROUPS * TM_GROUP_THREADS;
+constexpr int TM_NTW = 6, TM_MT = 2, TM_TE = TM_MT * 8;
+constexpr int TM_MAX_COLS = TM_GROUP_WARPS * TM_NTW * 8;          // 384 packed columns
+static_assert(TM_NTW == 6, "the inner loop fetches six fragment entries per k-step as four plus two doubles");
+constexpr int TM_WARP_COLUMNS = (QN / 4) * TM_NTW * 2;            // 192 32-bit columns per thread
+constexpr uint32_t TM_ALLOC_COLUMNS = 512;
+constexpr int TM_IMAGES = 2;                                        // images per group, used alternately
+
+struct TmemSymLayout
+{
+    int ldb, b_off, img_off, img_bytes, bar_off, slot_off, total;     // byte offsets into dynamic shared memory
+};
+
+__host__ __device__ inline TmemSymLayout tmem_sym_layout(int ni)
+{
+    TmemSymLayout l;
+    l.ldb = ni;
+    while (l.ldb % 8 != 4) ++l.ldb;
+    const int w_bytes = TM_GROUPS * 2 * TM_TE * LDW * 8;
+    l.b_off = w_bytes;
+    const int b_bytes = ((QN * l.ldb * 8 + 127) / 128) * 128;
+    // B is needed only until the right operand is parked in tensor memory: the images take its place afterwards
+    l.img_off = l.b_off;
+    l.img_bytes = ((8 * ni * ni * 8 + 127) / 128) * 128;
+    const int img_all = TM_GROUPS * TM_IMAGES * l.img_bytes;
+    l.bar_off = l.b_off + (img_all > b_bytes ? img_all : b_bytes);
+    l.slot_off = l.bar_off + TM_GROUPS * 2 * 8;
+    l.total = l.slot_off + 16;
+    return l;
+}
+
+template <int QC>
+__global__ void __launch_bounds__(TM_THREADS, 1)
+rank1_gemm_sym_tmem_kernel(const Rank1Args a)
+{
+    constexpr int NTW = TM_NTW, MT = TM_MT, TE = TM_TE;
+    const int q_ext = QC > 0 ? QC : (a.q + 7) & ~7;     // k-steps are taken in pairs; the padding rows / columns are zero
+    extern __shared__ __align__(128) unsigned char raw[];
+    const int ni = a.ni, nc = ni * ni, n_cols = ni * (ni + 1) / 2;
+    const TmemSymLayout L = tmem_sym_layout(ni);
+    const int ldb = L.ldb;
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int group = warp >> 3, wg = warp & 7, gtid = tid & (TM_GROUP_THREADS - 1);
+
+    double *sW_all = reinterpret_cast<double *>(raw);                                   // [groups][2][TE * LDW]
+    double *sW = sW_all + group * 2 * TE * LDW;
+    double *sB = reinterpret_cast<double *>(raw + L.b_off);                             // [q_ext][ldb]
+    unsigned char *img_base = raw + L.img_off + group * TM_IMAGES * L.img_bytes;        // [images] 8 element matrices each
+    uint64_t *full = reinterpret_cast<uint64_t *>(raw + L.bar_off) + group * 2;         // [2]
+    uint32_t *slot = reinterpret_cast<uint32_t *>(raw + L.slot_off);
+
+    if (tid == 0)
+    {
+        for (int i = 0; i < TM_GROUPS * 2; ++i) mbar_init(reinterpret_cast<uint64_t *>(raw + L.bar_off) + i, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(slot, TM_ALLOC_COLUMNS);
+    for (int i = tid; i < q_ext * ni; i += TM_THREADS) sB[(i / ni) * ldb + (i % ni)] = i < a.q * ni ? a.B1[i] : 0.0;
+    {
+        const int pad = q_ext - a.q;      // the W rows of all four buffers are contiguous: rows 0 .. 4*TE-1
+        for (int i = tid; i < TM_GROUPS * 2 * TE * pad; i += TM_THREADS) sW_all[(i / pad) * LDW + a.q + i % pad] = 0.0;
+    }
+    tmem_fence_before_sync();
+    __syncthreads();
+    tmem_fence_after_sync();
+    const uint32_t tmem_base = *slot;
+    // this warp's lanes (its quarter of the 128) and its 192 columns (two warps of a group share a quarter)
+    const uint32_t tcol = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + static_cast<uint32_t>(((warp >> 2) & 1) * TM_WARP_COLUMNS);
+
+    // packed column c -> (i, j), row-major upper triangle; fixed per thread for the whole kernel
+    auto unpack = [&](int c, int &i, int &j) {
+        int row = 0, start = 0;
+        while (start + (ni - row) <= c) { start += ni - row; ++row; }
+        i = row;
+        j = row + (c - start);
+    };
+    // where this lane's two C-fragment columns of every column tile and their mirrors go in an element matrix:
+    // low half = position of (i,j), high half = position of (j,i); 0xFFFF = nothing to store
+    uint32_t pos[NTW][2];
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt)
+    {
+        const int cbase = (wg * NTW + nt) * 8;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+        {
+            const int cc = cbase + 2 * t + h;
+            uint32_t direct = 0xFFFFu, mirror = 0xFFFFu;
+            if (cc < n_cols)
+            {
+                int i, j;
+                unpack(cc, i, j);
+                direct = static_cast<uint32_t>(i * ni + j);
+                if (i != j) mirror = static_cast<uint32_t>(j * ni + i);
+            }
+            pos[nt][h] = direct | (mirror << 16);
+        }
+    }
+
+    if (group == 0)
+    {
+        // park this thread's fragment entries of BB: k-step ks, column tile nt at columns 12*ks + 2*nt (+1)
+        int off1[NTW], off2[NTW];
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt)
+        {
+            int c = (wg * NTW + nt) * 8 + g;
+            c = c < n_cols ? c : n_cols - 1;        // padded columns compute a copy that is never stored
+            unpack(c, off1[nt], off2[nt]);
+        }
+        for (int ks = 0; ks < q_ext / 4; ++ks)
+        {
+            const double *b = sB + (4 * ks + t) * ldb;
+            double v[NTW];
+#pragma unroll
+            for (int nt = 0; nt < NTW; ++nt) v[nt] = b[off1[nt]] * b[off2[nt]];
+#pragma unroll
+            for (int nt = 0; nt < NTW; nt += 2) tmem_store_2(tcol + ks * (2 * NTW) + 2 * nt, v[nt], v[nt + 1]);
+        }
+        tmem_wait_stores();
+    }
+    tmem_fence_before_sync();
+    __syncthreads();
+    tmem_fence_after_sync();
+
+    const int64_t n_tiles = (a.elements + TE - 1) / TE;
+    const int64_t stride = static_cast<int64_t>(TM_GROUPS) * gridDim.x;
+    auto issue_w = [&](int64_t tile, int buf) {
+        const int64_t e0 = tile * TE;
+        if (!a.use_bulk || e0 >= a.elements) return;
+        if (gtid < 32)
+        {
+            const int64_t left = a.elements - e0;
+            const int n_e = left < TE ? static_cast<int>(left) : TE;
+            if (gtid == 0) mbar_arrive_expect_tx(&full[buf], n_e * a.q * 8);
+            __syncwarp();
+            if (gtid < n_e) bulk_load(sW + buf * TE * LDW + gtid * LDW, a.W + (e0 + gtid) * a.q, a.q * 8, &full[buf]);
+        }
+    };
+
+    int64_t tile = static_cast<int64_t>(TM_GROUPS) * blockIdx.x + group;
+    issue_w(tile, 0);
+    uint32_t phase_bits = 0;
+    int buf = 0;
+    uint32_t round = 0;       // row tiles this group has finished (selects the image)
+    const bool bulk_out = aligned16(a.M);
+    const int bar_id = 1 + group;
+
+    for (; tile < n_tiles; tile += stride)
+    {
+        issue_w(tile + stride, buf ^ 1);     // released by the barriers that closed the previous tile
+        const int64_t e0 = tile * TE;
+        const int64_t left = a.elements - e0;
+        const int n_e = left < TE ? static_cast<int>(left) : TE;
+        if (a.use_bulk)
+        {
+            if (!mbar_wait(&full[buf], (phase_bits >> buf) & 1u)) atomicExch(a.wait_flag, 1);
+            phase_bits ^= (1u << buf);
+        }
+        else
+        {
+            for (int i = gtid; i < n_e * a.q; i += TM_GROUP_THREADS) sW[buf * TE * LDW + (i / a.q) * LDW + (i % a.q)] = __ldcs(a.W + e0 * a.q + i);
+            named_barrier(bar_id, TM_GROUP_THREADS);
+        }
+        const double *sw = sW + buf * TE * LDW;
+
+        double acc[MT][NTW][2];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NTW; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
+        // Twelve fragment entries (two k-steps x six column tiles) per fetch from tensor memory; the fetch latency is
+        // covered by the other warps of the SM sub-partition (fetching one k-step ahead into a second register set
+        // was measured 3 % slower).
+#pragma unroll 2
+        for (int kp = 0; kp < q_ext / 8; ++kp)
+        {
+            uint32_t fa[8], fb[8], fc[8];      // doubles 0..3, 4..7, 8..11: k-step 2*kp (0..5), then k-step 2*kp+1 (6..11)
+            tmem_load_4(tcol + kp * (4 * NTW), fa);
+            tmem_load_4(tcol + kp * (4 * NTW) + 8, fb);
+            tmem_load_4(tcol + kp * (4 * NTW) + 16, fc);
+            double af[2][MT];
+#pragma unroll
+            for (int s2 = 0; s2 < 2; ++s2)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) af[s2][mt] = sw[(mt * 8 + g) * LDW + kp * 8 + s2 * 4 + t];
+            tmem_wait_loads();
+            double bf[2][NTW];
+#pragma unroll
+            for (int d = 0; d < 4; ++d)
+            {
+                bf[0][d] = tmem_double(fa[2 * d], fa[2 * d + 1]);
+                (d < 2 ? bf[0][4 + d] : bf[1][d - 2]) = tmem_double(fb[2 * d], fb[2 * d + 1]);
+                bf[1][2 + d] = tmem_double(fc[2 * d], fc[2 * d + 1]);
+            }
+#pragma unroll
+            for (int s2 = 0; s2 < 2; ++s2)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < NTW; ++nt) dmma_m8n8k4(acc[mt][nt], af[s2][mt], bf[s2][nt]);
+        }
+
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+        {
+            const int rows = n_e - mt * 8 < 8 ? (n_e - mt * 8 > 0 ? n_e - mt * 8 : 0) : 8;   // valid elements of this row tile
+            // Row tile r goes through image r % 2.  The last store that read this image belongs to row tile r - 2; thread 0
+            // waited for it before the barrier of row tile r - 1, so every thread may write here without another barrier.
+            double *img = reinterpret_cast<double *>(img_base + (round % TM_IMAGES) * L.img_bytes);
+            double *row = img + g * nc;
+#pragma unroll
+            for (int nt = 0; nt < NTW; ++nt)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                {
+                    const uint32_t direct = pos[nt][h] & 0xFFFFu, mirror = pos[nt][h] >> 16;
+                    if (direct != 0xFFFFu) row[direct] = acc[mt][nt][h];
+                    if (mirror != 0xFFFFu) row[mirror] = acc[mt][nt][h];
+                }
+            fence_proxy_async();
+            if (gtid == 0) bulk_wait_read<0>();      // the store of the previous row tile (the other image) has read its image
+            named_barrier(bar_id, TM_GROUP_THREADS);
+            double *dst = a.M + (e0 + mt * 8) * nc;
+            if (bulk_out && rows == 8)
+            {
+                if (gtid == 0)
+                {
+                    bulk_store(dst, img, 8 * nc * 8);
+                    bulk_commit();
+                }
+            }
+            else
+            {
+                for (int i = gtid; i < rows * nc; i += TM_GROUP_THREADS) __stcs(dst + i, img[i]);
+                named_barrier(bar_id, TM_GROUP_THREADS);     // plain loads of the image: finished before it is written again
+            }
+            ++round;
+        }
+        buf ^= 1;
+    }
+    if (gtid == 0) bulk_wait_all<0>();   // shared memory must outlive the stores that read it
+    tmem_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_free(tmem_base, TM_ALLOC_COLUMNS);
+}
+
 typedef SymCfg<8, 6, 2, 1, 2> SymSmall;    // 256 threads, 16-element tiles, one image, two CTAs per SM
 
 }
@@ -438,7 +705,21 @@ int acro_b200_rank1_gemm(const double *W, const double *B1, const double *B2, do
 
     const size_t smem = sizeof(Smem);
     const int64_t n_tiles = (elements + ET - 1) / ET;
-    const bool symmetric = (B1 == B2 && ni == nj && op == ACRO_B200_OP_ASSIGN && ni * (ni + 1) / 2 <= SymSmall::MAX_COLS);
+    static_assert(TM_MAX_COLS == SymSmall::MAX_COLS, "both symmetric variants cover the same packed columns");
+    const bool symmetric = (B1 == B2 && ni == nj && op == ACRO_B200_OP_ASSIGN && ni * (ni + 1) / 2 <= TM_MAX_COLS);
+    static const bool old_variant = [] { const char *e = std::getenv("ACRO_B200_RANK1_OLD"); return e != nullptr && e[0] == '1'; }();
+    if (symmetric && !old_variant)
+    {
+        const TmemSymLayout L = tmem_sym_layout(ni);
+        auto tm_kernel = q == QN ? rank1_gemm_sym_tmem_kernel<QN> : rank1_gemm_sym_tmem_kernel<0>;
+        cudaError_t st = cudaFuncSetAttribute(tm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        if (st != cudaSuccess) return fail_cuda(st, "acro_b200_rank1_gemm (shared memory opt-in)");
+        const int64_t sym_tiles = (elements + TM_TE - 1) / TM_TE;
+        int64_t g1 = sms;
+        if (g1 > (sym_tiles + TM_GROUPS - 1) / TM_GROUPS) g1 = (sym_tiles + TM_GROUPS - 1) / TM_GROUPS;
+        tm_kernel<<<static_cast<int>(g1), TM_THREADS, L.total, as_stream(stream)>>>(args);
+        return launch_status("acro_b200_rank1_gemm (symmetric, tensor memory)");
+    }
     if (symmetric)
     {
         const SymLayout L = sym_layout(ni, SymSmall::TILE_E, SymSmall::IMAGES);
