@@ -25,6 +25,9 @@
 #include "common.cuh"
 #include "dmma.cuh"
 #include "tma.cuh"
+#include "tensormap.cuh"
+
+#include <cstdlib>
 
 using namespace acro_b200_detail;
 
@@ -436,6 +439,180 @@ int launch_ring(const GemmArgs &args, int trans_a, int trans_b, int sms, cudaStr
     return launch_status("acro_b200_batched_gemm");
 }
 
+// ------------------------------------------------------------------ 64 x 64 x 64 through tiled bulk copies
+// The same persistent CTA, ring and warp tiling as batched_gemm_kernel<64>, with every copy done by the copy
+// engine instead of by the threads.  An operand matrix arrives as eight tiled copies (tensor maps, boxes of
+// 8 columns x 64 rows = 4 KB) issued by one thread; the map's 64-byte swizzle takes the place of the padded rows:
+// a box is stored as 64 rows of 64 bytes and the 16-byte unit u of row r sits at unit u ^ ((r / 2) % 4), which
+// makes both fragment patterns of mma.sync m8n8k4 (8 rows x 4 consecutive doubles, 4 rows x 8 consecutive
+// doubles) free of bank conflicts, in either storage order of the operand.  The unpadded ring leaves room for a
+// staging area: every warp writes its 16 x 32 block of C there in the same swizzled layout and sends it off as
+// four tiled stores of its own, so warps still never meet at a CTA barrier.  What this removes from the
+// threads, per element: 32 sixteen-byte copy instructions with their address arithmetic, and 16 sixteen-byte
+// global stores.
+constexpr int T64 = 64;
+constexpr int T64_BOX = 8;                                   // columns per box (64 bytes: the swizzle span)
+constexpr int T64_MATRIX = T64 * T64;                        // doubles per operand matrix in the ring (unpadded)
+constexpr int T64_CHUNK = T64 * T64_BOX;                     // doubles per box of an operand
+constexpr int T64_RING_BYTES = STAGES * 2 * T64_MATRIX * 8;  // 196,608
+constexpr int T64_SMEM_BYTES = T64_RING_BYTES + 2 * STAGES * 8 + 1024;   // + barriers + alignment slack
+
+struct Tiled64Args
+{
+    double *C;
+    int64_t batch;
+    int op;
+    int *wait_flag;
+};
+
+// Offset (doubles) of entry (r, c) of a matrix stored as boxes of 8 columns, rows of 64 bytes, 64-byte swizzle.
+template <int ROWS>
+__device__ __forceinline__ int swz(int r, int c)
+{
+    return (c >> 3) * (ROWS * T64_BOX) + r * T64_BOX + ((((c >> 1) & 3) ^ ((r >> 1) & 3)) << 1) + (c & 1);
+}
+
+// Sixteen warps in two groups of eight.  The elements a CTA walks over go alternately to the two groups, each of
+// which tiles its element like the eight warps of batched_gemm_kernel<64> (16 x 32 of C per warp); the groups run
+// half an element apart, so that while one drains its accumulators, stores C and waits for its next operands the
+// other is in the middle of its tensor-core loop (with a single group the pipe idled 22 % of the time whatever the
+// copy mechanism, the number of warps or the depth of the prefetch).  The ring's three slots hold the two elements
+// being multiplied and the one in flight; a group's first thread refills the slot its own group read two elements
+// earlier, so neither group ever waits for the other.
+constexpr int T64_GROUPS = 2, T64_GROUP_WARPS = 8, T64_THREADS = T64_GROUPS * T64_GROUP_WARPS * 32;
+
+template <bool TA, bool TB>
+__global__ void __launch_bounds__(T64_THREADS, 1)
+batched_gemm64_tiled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Tiled64Args a)
+{
+    constexpr int N = T64, MT = 2, NTL = 4;
+    extern __shared__ unsigned char raw_unaligned[];
+    // the swizzle is a function of the shared-memory address: boxes must start on multiples of 512 bytes
+    unsigned char *raw = raw_unaligned + ((1024u - (smem_addr(raw_unaligned) & 1023u)) & 1023u);
+    double *ring = reinterpret_cast<double *>(raw);                                      // [STAGES][A | B][T64_MATRIX]
+    uint64_t *full = reinterpret_cast<uint64_t *>(raw + T64_RING_BYTES);
+    uint64_t *empty = full + STAGES;
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int group = warp / T64_GROUP_WARPS, wg = warp % T64_GROUP_WARPS;
+    const int m0 = (wg >> 1) * 16, n0 = (wg & 1) * 32;
+    const bool issuer = (wg == 0 && lane == 0);      // the thread of this group that starts copies
+
+    if (tid == 0)
+    {
+        for (int i = 0; i < STAGES; ++i)
+        {
+            mbar_init(&full[i], 1);                   // the issuing thread's arrival, which also announces the bytes
+            mbar_init(&empty[i], T64_GROUP_WARPS);    // one arrival per warp of the group that read the slot
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    auto issue = [&](int64_t j) {      // element number j of this CTA into slot j % STAGES
+        const int64_t e = blockIdx.x + j * gridDim.x;
+        if (e >= a.batch) return;
+        const int stage = static_cast<int>(j % STAGES);
+        mbar_arrive_expect_tx(&full[stage], 2 * T64_MATRIX * 8);
+        double *sa = ring + stage * 2 * T64_MATRIX, *sb = sa + T64_MATRIX;
+        const int y = static_cast<int>(e * N);
+#pragma unroll
+        for (int c = 0; c < N / T64_BOX; ++c) tensor_load_2d(sa + c * T64_CHUNK, &map_a, c * T64_BOX, y, &full[stage]);
+#pragma unroll
+        for (int c = 0; c < N / T64_BOX; ++c) tensor_load_2d(sb + c * T64_CHUNK, &map_b, c * T64_BOX, y, &full[stage]);
+    };
+    if (tid == 0)
+    {
+        issue(0);
+        issue(1);
+    }
+
+    // this group takes elements j = group, group + 2, ... of the CTA
+    for (int64_t j = group; blockIdx.x + j * gridDim.x < a.batch; j += T64_GROUPS)
+    {
+        const int64_t e = blockIdx.x + j * gridDim.x;
+        const int stage = static_cast<int>(j % STAGES);
+        if (issuer && j >= 1)
+        {
+            // element j + 1 (the other group's next one) goes to the slot this group read two elements ago
+            const int ns = static_cast<int>((j + 1) % STAGES);
+            const int64_t use = (j + 1) / STAGES;      // how often that slot was filled before
+            if (use > 0 && !mbar_wait(&empty[ns], static_cast<uint32_t>((use - 1) & 1))) atomicExch(a.wait_flag, 1);
+            issue(j + 1);
+        }
+        if (!mbar_wait(&full[stage], static_cast<uint32_t>((j / STAGES) & 1))) atomicExch(a.wait_flag, 1);
+
+        const double *sa = ring + stage * 2 * T64_MATRIX;
+        const double *sb = sa + T64_MATRIX;
+        double c[MT][NTL][2];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NTL; ++nt) c[mt][nt][0] = c[mt][nt][1] = 0.0;
+
+#pragma unroll 4
+        for (int k0 = 0; k0 < N; k0 += 4)
+        {
+            double af[MT], bf[NTL];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) af[mt] = TA ? sa[swz<N>(k0 + t, m0 + mt * 8 + g)] : sa[swz<N>(m0 + mt * 8 + g, k0 + t)];
+#pragma unroll
+            for (int nt = 0; nt < NTL; ++nt) bf[nt] = TB ? sb[swz<N>(n0 + nt * 8 + g, k0 + t)] : sb[swz<N>(k0 + t, n0 + nt * 8 + g)];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < NTL; ++nt) dmma_m8n8k4(c[mt][nt], af[mt], bf[nt]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[stage]);   // this warp no longer reads the slot
+
+        // C rows leave as 64-byte segments per quad (two doubles per lane)
+        double *gc = a.C + e * N * N;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NTL; ++nt)
+            {
+                double *dst = gc + (m0 + mt * 8 + g) * N + n0 + nt * 8 + 2 * t;
+                double v0 = c[mt][nt][0], v1 = c[mt][nt][1];
+                if (a.op == ACRO_B200_OP_ADD) { v0 += dst[0]; v1 += dst[1]; }
+                else if (a.op == ACRO_B200_OP_SUB) { v0 = dst[0] - v0; v1 = dst[1] - v1; }
+                __stcs(reinterpret_cast<double2 *>(dst), make_double2(v0, v1));
+            }
+    }
+}
+
+template <bool TA, bool TB>
+int launch_tiled64_as(const CUtensorMap &ma, const CUtensorMap &mb, const Tiled64Args &args, int sms, cudaStream_t stream)
+{
+    auto kernel = batched_gemm64_tiled_kernel<TA, TB>;
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T64_SMEM_BYTES);
+    if (status != cudaSuccess) return fail_cuda(status, "acro_b200_batched_gemm (shared memory opt-in)");
+    int64_t grid = sms;
+    if (grid > args.batch) grid = args.batch;
+    kernel<<<static_cast<int>(grid), T64_THREADS, T64_SMEM_BYTES, stream>>>(ma, mb, args);
+    return launch_status("acro_b200_batched_gemm (tiled copies)");
+}
+
+// Returns 1 when the tiled-copy kernel cannot be used for this call (the caller then takes the ring of thread copies).
+int launch_tiled64(const double *A, const double *B, double *C, int64_t batch, int trans_a, int trans_b, int op, int *wait_flag, int sms,
+                   cudaStream_t stream, int *status)
+{
+    if (!aligned16(A) || !aligned16(B) || !aligned16(C) || batch * T64 >= (int64_t(1) << 31)) return 1;
+    CUtensorMap ma, mb;
+    const uint64_t rows = static_cast<uint64_t>(batch) * T64;
+    if (!encode_matrix_map(&ma, A, rows, T64, T64_BOX, T64) || !encode_matrix_map(&mb, B, rows, T64, T64_BOX, T64)) return 1;
+    Tiled64Args args;
+    args.C = C;
+    args.batch = batch;
+    args.op = op;
+    args.wait_flag = wait_flag;
+    *status = trans_a ? (trans_b ? launch_tiled64_as<true, true>(ma, mb, args, sms, stream) : launch_tiled64_as<true, false>(ma, mb, args, sms, stream))
+                      : (trans_b ? launch_tiled64_as<false, true>(ma, mb, args, sms, stream) : launch_tiled64_as<false, false>(ma, mb, args, sms, stream));
+    return 0;
+}
+
 }
 
 extern "C" {
@@ -510,6 +687,12 @@ int acro_b200_batched_gemm_t(const double *A, const double *B, double *C, int64_
         // sizes 17..32; plain products with a larger extent went to the GEMM kernel above, transposed ones use the 64-wide slots
         if (m <= 32 && n <= 32 && k <= 32) return launch_padded<32>(pa, trans_a, trans_b, sms, as_stream(stream));
         return launch_padded<64>(pa, trans_a, trans_b, sms, as_stream(stream));
+    }
+    static const bool thread_copies = [] { const char *e = std::getenv("ACRO_B200_GEMM64_OLD"); return e != nullptr && e[0] == '1'; }();
+    if (m == 64 && !thread_copies)
+    {
+        int status = ACRO_B200_OK;
+        if (launch_tiled64(A, B, C, batch, trans_a, trans_b, op, args.wait_flag, sms, as_stream(stream), &status) == 0) return status;
     }
     return m == 64 ? launch_ring<64>(args, trans_a, trans_b, sms, as_stream(stream)) : launch_ring<32>(args, trans_a, trans_b, sms, as_stream(stream));
 }
