@@ -567,6 +567,11 @@ rank1_gemm_sym_tmem_kernel(const Rank1Args a)
     uint32_t phase_bits = 0;
     int buf = 0;
     uint32_t round = 0;       // row tiles this group has finished (selects the image)
+    // The two groups should run half a tile apart, one in its tensor-core loop while the other scatters and stores.
+    // Left alone they start together and only drift apart over many tiles; short launches never get there.  So group 1
+    // holds its first tile back until group 0 is half-way through the k-steps of its own first tile (named barrier 3,
+    // group 0 arriving without blocking; it arrives after its loop at the latest, so group 1 cannot be left waiting).
+    bool stagger_pending = true;
     const bool bulk_out = aligned16(a.M);
     const int bar_id = 1 + group;
 
@@ -587,6 +592,11 @@ rank1_gemm_sym_tmem_kernel(const Rank1Args a)
             named_barrier(bar_id, TM_GROUP_THREADS);
         }
         const double *sw = sW + buf * TE * LDW;
+        if (group == 1 && stagger_pending)
+        {
+            named_barrier(3, TM_THREADS);
+            stagger_pending = false;
+        }
 
         double acc[MT][NTW][2];
 #pragma unroll
@@ -599,6 +609,11 @@ rank1_gemm_sym_tmem_kernel(const Rank1Args a)
 #pragma unroll 2
         for (int kp = 0; kp < q_ext / 8; ++kp)
         {
+            if (group == 0 && stagger_pending && kp == q_ext / 16)
+            {
+                named_barrier_arrive(3, TM_THREADS);
+                stagger_pending = false;
+            }
             uint32_t fa[8], fb[8], fc[8];      // doubles 0..3, 4..7, 8..11: k-step 2*kp (0..5), then k-step 2*kp+1 (6..11)
             tmem_load_4(tcol + kp * (4 * NTW), fa);
             tmem_load_4(tcol + kp * (4 * NTW) + 8, fb);
@@ -663,6 +678,7 @@ rank1_gemm_sym_tmem_kernel(const Rank1Args a)
         }
         buf ^= 1;
     }
+    if (group == 0 && stagger_pending) named_barrier_arrive(3, TM_THREADS);     // no tile for this group at all
     if (gtid == 0) bulk_wait_all<0>();   // shared memory must outlive the stores that read it
     tmem_fence_before_sync();
     __syncthreads();

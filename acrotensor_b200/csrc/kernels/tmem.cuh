@@ -69,6 +69,9 @@ __device__ __forceinline__ double tmem_double(uint32_t lo, uint32_t hi) { return
 
 // CTA-local named barrier over `threads` threads (a multiple of 32); id 1..15 (0 is __syncthreads).
 __device__ __forceinline__ void named_barrier(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
+// One-way use of a named barrier: `threads` counts the arriving and the waiting threads together; the arriving
+// threads do not block.
+__device__ __forceinline__ void named_barrier_arrive(int id, int threads) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
 }
 
