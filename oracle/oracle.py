@@ -18,7 +18,8 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 PORT_SO = os.path.join(HERE, "libacro_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libacro_ref.so")
-REFERENCE_CHECKOUT = os.environ.get("ACRO_REFERENCE_DIR", "/root/reference")
+# the reference checkout: ACRO_REFERENCE_DIR, else a directory "reference" beside this repository
+REFERENCE_CHECKOUT = os.environ.get("ACRO_REFERENCE_DIR") or os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
 
 _libs = {}
 

@@ -12,7 +12,8 @@ import pytest
 import acrotensor_b200 as ab
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("ACRO_REFERENCE_DIR", "/root/reference")
+# the reference checkout: ACRO_REFERENCE_DIR, else a directory "reference" beside this repository
+REF = os.environ.get("ACRO_REFERENCE_DIR") or os.path.normpath(os.path.join(ROOT, "..", "reference"))
 LIBDIR = os.path.dirname(ab.LIB_PATH)
 
 
@@ -33,6 +34,26 @@ def api_check(tmp_path_factory):
 def test_cpp_api_host_side(api_check):
     res = subprocess.run([api_check], capture_output=True, text=True)
     assert res.returncode == 0 and "OK" in res.stdout, res.stdout + res.stderr
+
+
+def test_dropin_artefacts_link_like_the_reference_build(tmp_path):
+    """`make dropin` leaves lib/libacrotensor.a, lib/shared/libacrotensor.so and inc/*.hpp, the names the reference's
+    makefile produces; a program built against nothing but those (and the CUDA runtime) passes the host checks."""
+    prefix = tmp_path / "acro"
+    res = subprocess.run(["make", "-C", os.path.join(ROOT, "acrotensor_b200", "csrc"), "dropin", "PREFIX=" + str(prefix)],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]
+    for rel in ("lib/libacrotensor.a", "lib/shared/libacrotensor.so", "inc/AcroTensor.hpp", "inc/acro_b200.h"):
+        assert (prefix / rel).exists(), rel
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    exe = str(tmp_path / "api_static")
+    cmd = ["g++", "-std=c++17", "-O1", "-w", "-I" + str(prefix / "inc"), os.path.join(ROOT, "tests", "cpp", "api_check.cpp"),
+           "-L" + str(prefix / "lib"), "-l:libacrotensor.a", "-L" + os.path.join(cuda, "lib64"), "-lcudart_static", "-ldl", "-lrt", "-lpthread",
+           "-o", exe]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]
+    run = subprocess.run([exe], capture_output=True, text=True)
+    assert run.returncode == 0 and "OK" in run.stdout, run.stdout + run.stderr
 
 
 @pytest.mark.gpu
