@@ -25,9 +25,6 @@
 #include "common.cuh"
 #include "dmma.cuh"
 #include "tma.cuh"
-#include "tensormap.cuh"
-
-#include <cstdlib>
 
 using namespace acro_b200_detail;
 
@@ -439,113 +436,88 @@ int launch_ring(const GemmArgs &args, int trans_a, int trans_b, int sms, cudaStr
     return launch_status("acro_b200_batched_gemm");
 }
 
-// ------------------------------------------------------------------ 64 x 64 x 64 through tiled bulk copies
-// The same persistent CTA, ring and warp tiling as batched_gemm_kernel<64>, with every copy done by the copy
-// engine instead of by the threads.  An operand matrix arrives as eight tiled copies (tensor maps, boxes of
-// 8 columns x 64 rows = 4 KB) issued by one thread; the map's 64-byte swizzle takes the place of the padded rows:
-// a box is stored as 64 rows of 64 bytes and the 16-byte unit u of row r sits at unit u ^ ((r / 2) % 4), which
-// makes both fragment patterns of mma.sync m8n8k4 (8 rows x 4 consecutive doubles, 4 rows x 8 consecutive
-// doubles) free of bank conflicts, in either storage order of the operand.  The unpadded ring leaves room for a
-// staging area: every warp writes its 16 x 32 block of C there in the same swizzled layout and sends it off as
-// four tiled stores of its own, so warps still never meet at a CTA barrier.  What this removes from the
-// threads, per element: 32 sixteen-byte copy instructions with their address arithmetic, and 16 sixteen-byte
-// global stores.
-constexpr int T64 = 64;
-constexpr int T64_BOX = 8;                                   // columns per box (64 bytes: the swizzle span)
-constexpr int T64_MATRIX = T64 * T64;                        // doubles per operand matrix in the ring (unpadded)
-constexpr int T64_CHUNK = T64 * T64_BOX;                     // doubles per box of an operand
-constexpr int T64_RING_BYTES = STAGES * 2 * T64_MATRIX * 8;  // 196,608
-constexpr int T64_SMEM_BYTES = T64_RING_BYTES + 2 * STAGES * 8 + 1024;   // + barriers + alignment slack
+// ------------------------------------------------------------------ 64 x 64 x 64, two warp groups
+// Sixteen warps in two groups of eight over the same three-slot ring as batched_gemm_kernel<64>.  The elements a
+// CTA walks over go alternately to the two groups, each of which tiles its element like the eight warps of that
+// kernel (16 x 32 of C per warp); the groups run half an element apart, so that while one drains its accumulators,
+// stores C and waits for its next operands the other is in the middle of its tensor-core loop.  With a single
+// group the tensor pipe idled 22 % of the time whatever the copy mechanism (thread copies or tiled bulk copies),
+// the number of warps (8 or 16 on one element) or the depth of the prefetch (one or two elements ahead): all of
+// those measured 0.293-0.295 ms at 2^14 elements, this 0.273 ms.  The ring's three slots hold the two elements
+// being multiplied and the one in flight; the threads of a group copy the element the OTHER group needs next into
+// the slot their own group read two elements earlier, so neither group ever waits for the other.
+//
+// Measured alternatives for the copies (2^14 elements / 2^11 elements; this kernel: 0.273 / 0.0455 ms): tiled bulk
+// copies through tensor maps into an unpadded ring, boxes of 8 columns x 64 rows with the 64-byte swizzle in place of
+// the padded rows: 0.267-0.271 / 0.0476 ms, with two-way bank conflicts left in the fragment loads (the hardware
+// serves an 8-byte load per half-warp, and rows g and g + 2 of a half-warp fall on the same banks; ncu: shared-memory
+// pipe 74 % busy); boxes of 4 columns x 64 rows without swizzle, which both fragment patterns read without conflicts:
+// 0.282 / 0.0516 ms (32-byte rows are too narrow for the copy engine).  Within 2 % of each other on long launches and
+// this one best on short ones, so the thread copies into padded rows stayed.
+constexpr int G2_GROUPS = 2, G2_GROUP_THREADS = NT, G2_THREADS = G2_GROUPS * G2_GROUP_THREADS;
 
-struct Tiled64Args
+// The threads of one group copy element e into slot `stage` (16 chunks of 16 bytes each per thread and operand)
+// and attach their arrivals on the slot's "full" barrier to the completion of those copies.
+__device__ __forceinline__ void issue_group_load(Smem<64> &s, const GemmArgs &a, int64_t e, int stage, int gtid)
 {
-    double *C;
-    int64_t batch;
-    int op;
-    int *wait_flag;
-};
-
-// Offset (doubles) of entry (r, c) of a matrix stored as boxes of 8 columns, rows of 64 bytes, 64-byte swizzle.
-template <int ROWS>
-__device__ __forceinline__ int swz(int r, int c)
-{
-    return (c >> 3) * (ROWS * T64_BOX) + r * T64_BOX + ((((c >> 1) & 3) ^ ((r >> 1) & 3)) << 1) + (c & 1);
+    constexpr int N = 64, LD = Smem<N>::LD, ROW_CHUNKS = N / 2;
+    const double *ga = a.A + e * N * N, *gb = a.B + e * N * N;
+#pragma unroll
+    for (int i = 0; i < N * ROW_CHUNKS / G2_GROUP_THREADS; ++i)
+    {
+        const int c = gtid + i * G2_GROUP_THREADS;
+        const int row = c / ROW_CHUNKS, col = (c % ROW_CHUNKS) * 2;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&s.A[stage][row * LD + col])), "l"(ga + c * 2) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&s.B[stage][row * LD + col])), "l"(gb + c * 2) : "memory");
+    }
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&s.full[stage])) : "memory");
 }
 
-// Sixteen warps in two groups of eight.  The elements a CTA walks over go alternately to the two groups, each of
-// which tiles its element like the eight warps of batched_gemm_kernel<64> (16 x 32 of C per warp); the groups run
-// half an element apart, so that while one drains its accumulators, stores C and waits for its next operands the
-// other is in the middle of its tensor-core loop (with a single group the pipe idled 22 % of the time whatever the
-// copy mechanism, the number of warps or the depth of the prefetch).  Holding group 1 back by half an element at the
-// start, so that short launches begin in that rhythm, changed nothing measurable here and is not done.  The ring's three slots hold the two elements
-// being multiplied and the one in flight; a group's first thread refills the slot its own group read two elements
-// earlier, so neither group ever waits for the other.
-constexpr int T64_GROUPS = 2, T64_GROUP_WARPS = 8, T64_THREADS = T64_GROUPS * T64_GROUP_WARPS * 32;
-
 template <bool TA, bool TB>
-__global__ void __launch_bounds__(T64_THREADS, 1)
-batched_gemm64_tiled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Tiled64Args a)
+__global__ void __launch_bounds__(G2_THREADS, 1)
+batched_gemm64_groups_kernel(const GemmArgs a)
 {
-    constexpr int N = T64, MT = 2, NTL = 4;
-    extern __shared__ unsigned char raw_unaligned[];
-    // the swizzle is a function of the shared-memory address: boxes must start on multiples of 512 bytes
-    unsigned char *raw = raw_unaligned + ((1024u - (smem_addr(raw_unaligned) & 1023u)) & 1023u);
-    double *ring = reinterpret_cast<double *>(raw);                                      // [STAGES][A | B][T64_MATRIX]
-    uint64_t *full = reinterpret_cast<uint64_t *>(raw + T64_RING_BYTES);
-    uint64_t *empty = full + STAGES;
+    constexpr int N = 64, LD = Smem<N>::LD, MT = 2, NTL = 4;
+    extern __shared__ __align__(128) unsigned char raw[];
+    Smem<N> &s = *reinterpret_cast<Smem<N> *>(raw);
     const int tid = threadIdx.x;
-    const int warp = tid >> 5, lane = tid & 31;
+    const int lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int group = warp / T64_GROUP_WARPS, wg = warp % T64_GROUP_WARPS;
+    const int group = tid / G2_GROUP_THREADS, gtid = tid % G2_GROUP_THREADS, wg = gtid >> 5;
     const int m0 = (wg >> 1) * 16, n0 = (wg & 1) * 32;
-    const bool issuer = (wg == 0 && lane == 0);      // the thread of this group that starts copies
 
     if (tid == 0)
     {
         for (int i = 0; i < STAGES; ++i)
         {
-            mbar_init(&full[i], 1);                   // the issuing thread's arrival, which also announces the bytes
-            mbar_init(&empty[i], T64_GROUP_WARPS);    // one arrival per warp of the group that read the slot
+            mbar_init(&s.full[i], G2_GROUP_THREADS);    // the copying group's threads
+            mbar_init(&s.empty[i], G2_GROUP_THREADS);   // the reading group's threads
         }
         fence_mbar_init();
     }
     __syncthreads();
 
-    auto issue = [&](int64_t j) {      // element number j of this CTA into slot j % STAGES
-        const int64_t e = blockIdx.x + j * gridDim.x;
-        if (e >= a.batch) return;
-        const int stage = static_cast<int>(j % STAGES);
-        mbar_arrive_expect_tx(&full[stage], 2 * T64_MATRIX * 8);
-        double *sa = ring + stage * 2 * T64_MATRIX, *sb = sa + T64_MATRIX;
-        const int y = static_cast<int>(e * N);
-#pragma unroll
-        for (int c = 0; c < N / T64_BOX; ++c) tensor_load_2d(sa + c * T64_CHUNK, &map_a, c * T64_BOX, y, &full[stage]);
-#pragma unroll
-        for (int c = 0; c < N / T64_BOX; ++c) tensor_load_2d(sb + c * T64_CHUNK, &map_b, c * T64_BOX, y, &full[stage]);
-    };
-    if (tid == 0)
-    {
-        issue(0);
-        issue(1);
-    }
+    // element number j of this CTA is element blockIdx.x + j * gridDim.x of the batch, lives in slot j % STAGES and
+    // belongs to group j % 2; the first two are copied by the groups that will read them
+    auto element_of = [&](int64_t j) { return blockIdx.x + j * gridDim.x; };
+    if (element_of(group) < a.batch) issue_group_load(s, a, element_of(group), group, gtid);
 
-    // this group takes elements j = group, group + 2, ... of the CTA
-    for (int64_t j = group; blockIdx.x + j * gridDim.x < a.batch; j += T64_GROUPS)
+    for (int64_t j = group; element_of(j) < a.batch; j += G2_GROUPS)
     {
-        const int64_t e = blockIdx.x + j * gridDim.x;
+        const int64_t e = element_of(j);
         const int stage = static_cast<int>(j % STAGES);
-        if (issuer && j >= 1)
+        if (j >= 1 && element_of(j + 1) < a.batch)
         {
             // element j + 1 (the other group's next one) goes to the slot this group read two elements ago
             const int ns = static_cast<int>((j + 1) % STAGES);
             const int64_t use = (j + 1) / STAGES;      // how often that slot was filled before
-            if (use > 0 && !mbar_wait(&empty[ns], static_cast<uint32_t>((use - 1) & 1))) atomicExch(a.wait_flag, 1);
-            issue(j + 1);
+            if (use > 0 && !mbar_wait(&s.empty[ns], static_cast<uint32_t>((use - 1) & 1))) atomicExch(a.wait_flag, 1);
+            issue_group_load(s, a, element_of(j + 1), ns, gtid);
         }
-        if (!mbar_wait(&full[stage], static_cast<uint32_t>((j / STAGES) & 1))) atomicExch(a.wait_flag, 1);
+        if (!mbar_wait(&s.full[stage], static_cast<uint32_t>((j / STAGES) & 1))) atomicExch(a.wait_flag, 1);
 
-        const double *sa = ring + stage * 2 * T64_MATRIX;
-        const double *sb = sa + T64_MATRIX;
+        const double *sa = s.A[stage];
+        const double *sb = s.B[stage];
         double c[MT][NTL][2];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
@@ -557,16 +529,15 @@ batched_gemm64_tiled_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         {
             double af[MT], bf[NTL];
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) af[mt] = TA ? sa[swz<N>(k0 + t, m0 + mt * 8 + g)] : sa[swz<N>(m0 + mt * 8 + g, k0 + t)];
+            for (int mt = 0; mt < MT; ++mt) af[mt] = frag_a<LD, TA>(sa, m0 + mt * 8 + g, k0 + t);
 #pragma unroll
-            for (int nt = 0; nt < NTL; ++nt) bf[nt] = TB ? sb[swz<N>(n0 + nt * 8 + g, k0 + t)] : sb[swz<N>(k0 + t, n0 + nt * 8 + g)];
+            for (int nt = 0; nt < NTL; ++nt) bf[nt] = frag_b<LD, TB>(sb, k0 + t, n0 + nt * 8 + g);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                 for (int nt = 0; nt < NTL; ++nt) dmma_m8n8k4(c[mt][nt], af[mt], bf[nt]);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[stage]);   // this warp no longer reads the slot
+        mbar_arrive(&s.empty[stage]);   // this thread no longer reads the slot
 
         // C rows leave as 64-byte segments per quad (two doubles per lane)
         double *gc = a.C + e * N * N;
@@ -579,40 +550,25 @@ batched_gemm64_tiled_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 double v0 = c[mt][nt][0], v1 = c[mt][nt][1];
                 if (a.op == ACRO_B200_OP_ADD) { v0 += dst[0]; v1 += dst[1]; }
                 else if (a.op == ACRO_B200_OP_SUB) { v0 = dst[0] - v0; v1 = dst[1] - v1; }
-                __stcs(reinterpret_cast<double2 *>(dst), make_double2(v0, v1));
+                if (aligned16(a.C)) __stcs(reinterpret_cast<double2 *>(dst), make_double2(v0, v1));
+                else { __stcs(dst, v0); __stcs(dst + 1, v1); }
             }
     }
 }
 
-template <bool TA, bool TB>
-int launch_tiled64_as(const CUtensorMap &ma, const CUtensorMap &mb, const Tiled64Args &args, int sms, cudaStream_t stream)
+int launch_groups64(const GemmArgs &args, int trans_a, int trans_b, int sms, cudaStream_t stream)
 {
-    auto kernel = batched_gemm64_tiled_kernel<TA, TB>;
-    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T64_SMEM_BYTES);
+    const size_t smem = sizeof(Smem<64>);
+    auto kernel = trans_a ? (trans_b ? batched_gemm64_groups_kernel<true, true> : batched_gemm64_groups_kernel<true, false>)
+                          : (trans_b ? batched_gemm64_groups_kernel<false, true> : batched_gemm64_groups_kernel<false, false>);
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (status != cudaSuccess) return fail_cuda(status, "acro_b200_batched_gemm (shared memory opt-in)");
     int64_t grid = sms;
     if (grid > args.batch) grid = args.batch;
-    kernel<<<static_cast<int>(grid), T64_THREADS, T64_SMEM_BYTES, stream>>>(ma, mb, args);
-    return launch_status("acro_b200_batched_gemm (tiled copies)");
+    kernel<<<static_cast<int>(grid), G2_THREADS, smem, stream>>>(args);
+    return launch_status("acro_b200_batched_gemm (two groups)");
 }
 
-// Returns 1 when the tiled-copy kernel cannot be used for this call (the caller then takes the ring of thread copies).
-int launch_tiled64(const double *A, const double *B, double *C, int64_t batch, int trans_a, int trans_b, int op, int *wait_flag, int sms,
-                   cudaStream_t stream, int *status)
-{
-    if (!aligned16(A) || !aligned16(B) || !aligned16(C) || batch * T64 >= (int64_t(1) << 31)) return 1;
-    CUtensorMap ma, mb;
-    const uint64_t rows = static_cast<uint64_t>(batch) * T64;
-    if (!encode_matrix_map(&ma, A, rows, T64, T64_BOX, T64) || !encode_matrix_map(&mb, B, rows, T64, T64_BOX, T64)) return 1;
-    Tiled64Args args;
-    args.C = C;
-    args.batch = batch;
-    args.op = op;
-    args.wait_flag = wait_flag;
-    *status = trans_a ? (trans_b ? launch_tiled64_as<true, true>(ma, mb, args, sms, stream) : launch_tiled64_as<true, false>(ma, mb, args, sms, stream))
-                      : (trans_b ? launch_tiled64_as<false, true>(ma, mb, args, sms, stream) : launch_tiled64_as<false, false>(ma, mb, args, sms, stream));
-    return 0;
-}
 
 }
 
@@ -689,12 +645,8 @@ int acro_b200_batched_gemm_t(const double *A, const double *B, double *C, int64_
         if (m <= 32 && n <= 32 && k <= 32) return launch_padded<32>(pa, trans_a, trans_b, sms, as_stream(stream));
         return launch_padded<64>(pa, trans_a, trans_b, sms, as_stream(stream));
     }
-    static const bool thread_copies = [] { const char *e = std::getenv("ACRO_B200_GEMM64_OLD"); return e != nullptr && e[0] == '1'; }();
-    if (m == 64 && !thread_copies)
-    {
-        int status = ACRO_B200_OK;
-        if (launch_tiled64(A, B, C, batch, trans_a, trans_b, op, args.wait_flag, sms, as_stream(stream), &status) == 0) return status;
-    }
+    // 64^3 with 16-byte aligned operands: two warp groups per CTA; unaligned operands keep the one-group kernel and its plain loads
+    if (m == 64 && args.async_copy) return launch_groups64(args, trans_a, trans_b, sms, as_stream(stream));
     return m == 64 ? launch_ring<64>(args, trans_a, trans_b, sms, as_stream(stream)) : launch_ring<32>(args, trans_a, trans_b, sms, as_stream(stream));
 }
 

@@ -84,23 +84,6 @@ __device__ __forceinline__ void bulk_store(void *gmem_dst, const void *smem_src,
 
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
-// Tiled copies through a tensor map (a 2-D view of global memory with a box size and a shared-memory swizzle fixed
-// at encoding time).  x is the coordinate along the contiguous dimension, in elements: x times the element size must
-// be a multiple of 16 bytes.  Loads complete on `bar` (bytes), stores belong to the issuing thread's bulk group.
-__device__ __forceinline__ void tensor_load_2d(void *smem_dst, const void *tensor_map, int x, int y, uint64_t *bar)
-{
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_addr(smem_dst)),
-                 "l"(tensor_map), "r"(x), "r"(y), "r"(smem_addr(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ void tensor_store_2d(const void *tensor_map, int x, int y, const void *smem_src)
-{
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tensor_map), "r"(x), "r"(y),
-                 "r"(smem_addr(smem_src))
-                 : "memory");
-}
-
 // Waits until at most N of this thread's bulk groups still READ their shared-memory source.
 template <int N>
 __device__ __forceinline__ void bulk_wait_read()
