@@ -234,10 +234,6 @@ static int launch_reduce(const double *A, const double *w, double *out, int64_t 
     const int T = threads_for(F);
     const int64_t tile_rows = 2 * static_cast<int64_t>(T) / F;
     const int64_t tiles = (rows + tile_rows - 1) / tile_rows;
-    int64_t grid = static_cast<int64_t>(sms) * (2048 / T > 0 ? 2048 / T : 1);
-    if (grid > tiles) grid = tiles;
-    if (grid > kMaxGrid) grid = kMaxGrid;
-    if (grid < 1) grid = 1;
 
     ReduceArgs args;
     args.A = A;
@@ -268,32 +264,22 @@ static int launch_reduce(const double *A, const double *w, double *out, int64_t 
     }
     const size_t smem = 2 * static_cast<size_t>(T) * sizeof(double);
     const bool vec = aligned16(A);
-    const int g = static_cast<int>(grid);
-    if (group != nullptr)
-    {
-        if (w != nullptr)
-        {
-            if (vec) reduce_batch_kernel<true, true, true><<<g, T, smem, s>>>(args, pv);
-            else reduce_batch_kernel<true, false, true><<<g, T, smem, s>>>(args, pv);
-        }
-        else
-        {
-            if (vec) reduce_batch_kernel<false, true, true><<<g, T, smem, s>>>(args, pv);
-            else reduce_batch_kernel<false, false, true><<<g, T, smem, s>>>(args, pv);
-        }
-        return launch_status("acro_b200_reduce_batch_allreduce");
-    }
-    if (w != nullptr)
-    {
-        if (vec) reduce_batch_kernel<true, true, false><<<g, T, smem, s>>>(args, pv);
-        else reduce_batch_kernel<true, false, false><<<g, T, smem, s>>>(args, pv);
-    }
-    else
-    {
-        if (vec) reduce_batch_kernel<false, true, false><<<g, T, smem, s>>>(args, pv);
-        else reduce_batch_kernel<false, false, false><<<g, T, smem, s>>>(args, pv);
-    }
-    return launch_status("acro_b200_reduce_batch");
+    typedef void (*kernel_t)(const ReduceArgs, const PeerView);
+    const kernel_t kernel = group != nullptr
+                                ? (w != nullptr ? (vec ? reduce_batch_kernel<true, true, true> : reduce_batch_kernel<true, false, true>)
+                                                : (vec ? reduce_batch_kernel<false, true, true> : reduce_batch_kernel<false, false, true>))
+                                : (w != nullptr ? (vec ? reduce_batch_kernel<true, true, false> : reduce_batch_kernel<true, false, false>)
+                                                : (vec ? reduce_batch_kernel<false, true, false> : reduce_batch_kernel<false, false, false>));
+    // One CTA per slot the SMs offer this kernel (registers allow two or three CTAs of this size per SM): every CTA
+    // is resident from the start and walks its share of the tiles, so there is no second wave of CTAs half-way through.
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, T, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+    int64_t grid = static_cast<int64_t>(sms) * per_sm;
+    if (grid > tiles) grid = tiles;
+    if (grid > kMaxGrid) grid = kMaxGrid;
+    if (grid < 1) grid = 1;
+    kernel<<<static_cast<int>(grid), T, smem, s>>>(args, pv);
+    return launch_status(group != nullptr ? "acro_b200_reduce_batch_allreduce" : "acro_b200_reduce_batch");
 }
 
 int acro_b200_reduce_batch(const double *A, const double *w, double *out, int64_t rows, int F, int op,
