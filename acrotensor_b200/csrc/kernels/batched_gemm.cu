@@ -473,7 +473,10 @@ __device__ __forceinline__ void issue_group_load(Smem<64> &s, const GemmArgs &a,
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&s.full[stage])) : "memory");
 }
 
-template <bool TA, bool TB>
+// ACC: the products of all elements a group walks over are summed in its accumulators and the group stores one
+// 64 x 64 tile of partial sums at C + (2 * blockIdx.x + group) * 64 * 64 when it is done (the Gram form; every group
+// of every CTA writes its tile, zeros if it had no element).
+template <bool TA, bool TB, bool ACC = false>
 __global__ void __launch_bounds__(G2_THREADS, 1)
 batched_gemm64_groups_kernel(const GemmArgs a)
 {
@@ -502,6 +505,12 @@ batched_gemm64_groups_kernel(const GemmArgs a)
     auto element_of = [&](int64_t j) { return blockIdx.x + j * gridDim.x; };
     if (element_of(group) < a.batch) issue_group_load(s, a, element_of(group), group, gtid);
 
+    double c[MT][NTL][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt) c[mt][nt][0] = c[mt][nt][1] = 0.0;
+
     for (int64_t j = group; element_of(j) < a.batch; j += G2_GROUPS)
     {
         const int64_t e = element_of(j);
@@ -518,11 +527,13 @@ batched_gemm64_groups_kernel(const GemmArgs a)
 
         const double *sa = s.A[stage];
         const double *sb = s.B[stage];
-        double c[MT][NTL][2];
+        if (!ACC)
+        {
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int nt = 0; nt < NTL; ++nt) c[mt][nt][0] = c[mt][nt][1] = 0.0;
+                for (int nt = 0; nt < NTL; ++nt) c[mt][nt][0] = c[mt][nt][1] = 0.0;
+        }
 
 #pragma unroll 4
         for (int k0 = 0; k0 < N; k0 += 4)
@@ -538,6 +549,7 @@ batched_gemm64_groups_kernel(const GemmArgs a)
                 for (int nt = 0; nt < NTL; ++nt) dmma_m8n8k4(c[mt][nt], af[mt], bf[nt]);
         }
         mbar_arrive(&s.empty[stage]);   // this thread no longer reads the slot
+        if (ACC) continue;
 
         // C rows leave as 64-byte segments per quad (two doubles per lane)
         double *gc = a.C + e * N * N;
@@ -552,6 +564,19 @@ batched_gemm64_groups_kernel(const GemmArgs a)
                 else if (a.op == ACRO_B200_OP_SUB) { v0 = dst[0] - v0; v1 = dst[1] - v1; }
                 if (aligned16(a.C)) __stcs(reinterpret_cast<double2 *>(dst), make_double2(v0, v1));
                 else { __stcs(dst, v0); __stcs(dst + 1, v1); }
+            }
+    }
+    if (ACC)
+    {
+        double *gc = a.C + (static_cast<int64_t>(G2_GROUPS) * blockIdx.x + group) * N * N;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NTL; ++nt)
+            {
+                double *dst = gc + (m0 + mt * 8 + g) * N + n0 + nt * 8 + 2 * t;
+                dst[0] = c[mt][nt][0];
+                dst[1] = c[mt][nt][1];
             }
     }
 }
@@ -611,6 +636,14 @@ int acro_b200_batched_gemm_t(const double *A, const double *B, double *C, int64_
                                       static_cast<int64_t>(m) * n, op, stream);
     }
     if (batched_gemm_small_supported(m, n, k)) return batched_gemm_small_launch(A, B, C, batch, m, n, k, trans_a, trans_b, op, as_stream(stream));
+    if (batch >= 2 && batched_gemm_pairs_supported(m, n, k, trans_a, trans_b) && aligned16(A) && aligned16(B) && aligned16(C))
+    {
+        // rows of an odd length: pairs of elements travel by bulk copy; an odd last element goes through the padded ring below
+        const int rc = batched_gemm_pairs_launch(A, B, C, batch / 2, m, n, k, trans_a, trans_b, op, as_stream(stream));
+        if (rc != ACRO_B200_OK || batch % 2 == 0) return rc;
+        const int64_t done = batch - 1;
+        return acro_b200_batched_gemm_t(A + done * m * k, B + done * k * n, C + done * m * n, 1, m, n, k, trans_a, trans_b, op, stream);
+    }
     const int sms = sm_count();
     if (sms <= 0) return fail_cuda(cudaErrorNoDevice, "acro_b200_batched_gemm");
 
@@ -694,6 +727,22 @@ int acro_b200_gram(const double *X, const double *Y, double *S, int64_t rows, in
 
     const bool big = a > 32 || b > 32;
     const int slab = big ? 64 : 32;
+    int parts = 0;
+    if (!big && rows >= 2 * slab && batched_gemm_pairs_supported(a, b, slab, 1, 0) && aligned16(X) && aligned16(Y))
+    {
+        // odd row lengths (27 x 27 ...): pairs of 32-row slabs by bulk copy; what is left (fewer than 64 rows) goes through the ring below
+        const int64_t pairs = rows / (2 * slab);
+        const int rc = gram_pairs_launch(X, Y, scratch, pairs, slab, a, b, kGramMaxParts - 3, &parts, st);
+        if (rc != ACRO_B200_OK) return rc;
+        X += pairs * 2 * slab * a;
+        Y += pairs * 2 * slab * b;
+        rows -= pairs * 2 * slab;
+        if (rows == 0)
+        {
+            gram_combine_kernel<<<(entries + 255) / 256, 256, 0, st>>>(S, scratch, parts, entries, op);
+            return launch_status("acro_b200_gram (combine)");
+        }
+    }
     const int64_t slabs = rows / slab;
     const int tail = static_cast<int>(rows - slabs * slab);
     auto kernel = big ? batched_gemm_padded_kernel<64, true, false, true> : batched_gemm_padded_kernel<32, true, false, true>;
@@ -708,22 +757,44 @@ int acro_b200_gram(const double *X, const double *Y, double *S, int64_t rows, in
     pa.cols_a = a;
     pa.cols_b = b;
     pa.wait_flag = wait_flag;
-    int parts = 0;
-    if (slabs > 0)
+    if (slabs > 0 && a == 64 && b == 64 && aligned16(X) && aligned16(Y))
+    {
+        // full 64 x 64 slabs fill the ring's slots exactly: the two-group kernel of the batched 64^3 product, accumulating
+        // (X_slab stored k x m: first operand transposed); one tile of partial sums per group
+        auto gk = batched_gemm64_groups_kernel<true, false, true>;
+        status = cudaFuncSetAttribute(gk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(Smem<64>)));
+        if (status != cudaSuccess) return fail_cuda(status, "acro_b200_gram (shared memory opt-in)");
+        int64_t grid = sms;
+        if (grid > slabs) grid = slabs;
+        if (G2_GROUPS * grid > kGramMaxParts - 1) grid = (kGramMaxParts - 1) / G2_GROUPS;
+        GemmArgs ga;
+        ga.A = X;
+        ga.B = Y;
+        ga.C = scratch;
+        ga.batch = slabs;
+        ga.op = ACRO_B200_OP_ASSIGN;
+        ga.wait_flag = wait_flag;
+        ga.async_copy = 1;
+        gk<<<static_cast<int>(grid), G2_THREADS, sizeof(Smem<64>), st>>>(ga);
+        const int launched = launch_status("acro_b200_gram (two groups)");
+        if (launched != ACRO_B200_OK) return launched;
+        parts = static_cast<int>(G2_GROUPS * grid);
+    }
+    else if (slabs > 0)
     {
         int64_t grid = static_cast<int64_t>(sms) * (big ? 1 : 4);
         if (grid > slabs) grid = slabs;
         if (grid > kGramMaxParts - 1) grid = kGramMaxParts - 1;
         pa.A = X;
         pa.B = Y;
-        pa.C = scratch;
+        pa.C = scratch + static_cast<int64_t>(parts) * entries;
         pa.batch = slabs;
         pa.k = pa.rows_a = pa.rows_b = slab;
         pa.wide = (aligned16(X) && aligned16(Y) && a % 2 == 0 && b % 2 == 0) ? 1 : 0;
         kernel<<<static_cast<int>(grid), NT, smem, st>>>(pa);
         const int launched = launch_status("acro_b200_gram");
         if (launched != ACRO_B200_OK) return launched;
-        parts = static_cast<int>(grid);
+        parts += static_cast<int>(grid);
     }
     if (tail > 0)
     {

@@ -52,6 +52,14 @@ int batched_matvec_launch(const double *M, const double *X, double *Y, int64_t b
 bool gram_stream_supported(int a, int b);
 int gram_stream_launch(const double *X, const double *Y, double *partials, int64_t rows, int a, int b, int max_parts, int *parts, cudaStream_t stream);
 
+// Pairs of elements by bulk copy for matrices of 17 .. 32 with rows of an odd length (batched_gemm_pairs.cu); the Gram form
+// over pairs of row slabs writes 2 * grid partial tiles (*parts) at partials.
+bool batched_gemm_pairs_supported(int m, int n, int k, int trans_a, int trans_b);
+int batched_gemm_pairs_launch(const double *A, const double *B, double *C, int64_t pairs, int m, int n, int k, int trans_a, int trans_b, int op,
+                              cudaStream_t stream);
+int gram_pairs_launch(const double *X, const double *Y, double *partials, int64_t pairs, int slab_rows, int a, int b, int max_parts, int *parts,
+                      cudaStream_t stream);
+
 __host__ __device__ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }

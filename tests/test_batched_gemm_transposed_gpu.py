@@ -45,7 +45,8 @@ CASES = [
     (1000, 3, 3, 3, 1, 0, 0, 0), (1000, 3, 3, 3, 0, 1, 0, 0), (4097, 4, 4, 4, 1, 1, 1, 0), (513, 8, 8, 8, 0, 1, 2, 0),
     (2050, 16, 16, 16, 1, 0, 0, 0), (777, 16, 16, 16, 1, 1, 1, 1), (300, 5, 7, 3, 1, 1, 0, 0), (64, 2, 16, 9, 0, 1, 2, 1), (33, 16, 15, 16, 1, 0, 0, 1),
     # zero-padded into 32-wide slots
-    (500, 27, 27, 27, 1, 0, 0, 0), (301, 27, 27, 27, 0, 1, 1, 1), (64, 20, 24, 30, 1, 1, 0, 0), (55, 18, 24, 31, 1, 0, 2, 0), (90, 17, 32, 5, 0, 1, 0, 0),
+    (500, 27, 27, 27, 1, 0, 0, 0), (301, 27, 27, 27, 0, 1, 1, 1), (1000, 27, 27, 27, 1, 1, 2, 0), (222, 25, 31, 19, 1, 0, 0, 0), (223, 21, 17, 29, 0, 1, 1, 0),
+    (90, 27, 23, 32, 1, 1, 0, 0), (64, 20, 24, 30, 1, 1, 0, 0), (55, 18, 24, 31, 1, 0, 2, 0), (90, 17, 32, 5, 0, 1, 0, 0),
     # the full 32-wide and 64-wide slots
     (200, 32, 32, 32, 1, 0, 0, 0), (201, 32, 32, 32, 1, 1, 1, 0), (150, 64, 64, 64, 0, 1, 0, 0), (149, 64, 64, 64, 1, 0, 2, 0), (33, 64, 64, 64, 1, 1, 0, 1),
     # zero-padded into 64-wide slots

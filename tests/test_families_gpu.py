@@ -128,6 +128,9 @@ def test_small_batched_gemm_kernel_is_bit_identical(torch, batch, m, n, k, op, o
 @pytest.mark.parametrize("batch,m,n,k,op,offset", [
     (1, 27, 27, 27, 0, 0), (500, 27, 27, 27, 0, 0), (301, 27, 27, 27, 1, 1), (64, 20, 33, 17, 0, 0), (40, 64, 64, 48, 2, 0), (90, 17, 64, 5, 0, 0),
     (75, 33, 1, 64, 0, 1), (130, 48, 48, 48, 1, 0), (55, 18, 24, 30, 0, 0), (33, 32, 32, 31, 0, 0), (20, 63, 63, 63, 0, 1),
+    # rows of an odd length, 17 .. 32: pairs of elements by bulk copy (an odd last element goes through the padded ring)
+    (2, 27, 27, 27, 0, 0), (3, 27, 27, 27, 0, 0), (1301, 27, 27, 27, 2, 0), (640, 17, 19, 21, 0, 0), (77, 31, 29, 23, 1, 0), (250, 9, 25, 31, 0, 0),
+    (300, 32, 27, 27, 0, 0), (123, 20, 31, 5, 2, 0),
     # above 64: tiles of every product through the GEMM kernel (odd sizes: shifted rows, 8-byte copies, ragged tiles)
     (7, 125, 125, 125, 0, 0), (5, 125, 125, 125, 1, 1), (3, 65, 200, 33, 2, 0), (4, 128, 64, 96, 0, 0), (9, 100, 3, 129, 0, 0),
     # matrix-vector forms on operands that are not 16-byte aligned (8-byte copies), ragged last tile

@@ -35,7 +35,11 @@ def to_dev(torch, arr, offset=0):
     (64 * 500, 64, 64, 0, 0), (64 * 500 + 37, 64, 64, 1, 0), (70001, 40, 64, 2, 0), (9999, 33, 7, 0, 1), (50, 64, 64, 0, 0),
     (32 * 3000, 8, 8, 0, 0), (100003, 8, 8, 1, 0), (100000, 5, 9, 2, 0), (77777, 27, 27, 0, 1), (31, 8, 8, 0, 0), (32, 16, 3, 0, 0),
     (77777, 16, 16, 0, 1), (50001, 6, 10, 0, 0), (70000, 13, 4, 1, 0), (2049, 16, 16, 2, 0), (600000, 2, 1, 0, 0),
-    (200001, 1, 1, 0, 0), (150000, 32, 1, 1, 0), (150000, 2, 32, 0, 1), (1, 3, 3, 0, 0), (400000, 3, 3, 0, 0)])
+    (200001, 1, 1, 0, 0), (150000, 32, 1, 1, 0), (150000, 2, 32, 0, 1), (1, 3, 3, 0, 0), (400000, 3, 3, 0, 0),
+    # odd row lengths on aligned operands: pairs of 32-row slabs by bulk copy, the rest through the ring
+    (77777, 27, 27, 0, 0), (64 * 700, 27, 27, 1, 0), (64 * 300 + 33, 25, 31, 2, 0), (130, 17, 19, 0, 0), (64, 27, 27, 0, 0), (63, 27, 27, 0, 0),
+    # full 64 x 64 slabs on the accumulating two-group kernel
+    (64 * 1000, 64, 64, 0, 0), (64 * 3 + 5, 64, 64, 1, 0), (64 * 149, 64, 64, 2, 0)])
 def test_gram_kernel(torch, rows, a, b, op, offset):
     rng = np.random.default_rng(rows + a + 3 * b)
     x, y = rng.standard_normal((rows, a)), rng.standard_normal((rows, b))
