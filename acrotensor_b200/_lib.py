@@ -92,6 +92,7 @@ SIGNATURES = {
     "acro_b200_batched_gemm_supported": (_I, [_I, _I, _I]),
     "acro_b200_batched_gemm": (_I, [_P, _P, _P, _I64, _I, _I, _I, _I, _P]),
     "acro_b200_batched_gemm_t_supported": (_I, [_I, _I, _I, _I, _I]),
+    "acro_b200_batched_gemm_by_pairs": (_I, [_I, _I, _I, _I, _I]),
     "acro_b200_batched_gemm_t": (_I, [_P, _P, _P, _I64, _I, _I, _I, _I, _I, _I, _P]),
     "acro_b200_gram_supported": (_I, [_I, _I]),
     "acro_b200_gram_scratch_bytes": (_SZ, [_I, _I]),

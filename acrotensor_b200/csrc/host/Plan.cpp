@@ -484,6 +484,8 @@ bool plan_batched_gemm(DimensionedKernel &k, int ki, Step &s)
     if (tb) note << " (second operand stored transposed)";
     if (m == 1 || n == 1) note << ", matrix-vector: streaming tiles of elements through shared memory (bulk copies), rows rotated across banks";
     else if (m <= 16 && n <= 16 && kn <= 16) note << ", streaming tiles of matrices through shared memory (bulk copies), 4x1 strips per thread, no fused multiply-add";
+    else if (acro_b200_batched_gemm_by_pairs(static_cast<int>(m), static_cast<int>(n), static_cast<int>(kn), ta, tb))
+        note << ", rows of an odd length: pairs of elements by bulk copy into unpadded slots, fp64 tensor cores (mma.sync m8n8k4); operands off a 16-byte boundary take the zero-padded ring";
     else if (!ta && !tb && (m > 32 || n > 32 || kn > 32) && !(m == 64 && n == 64 && kn == 64)) note << ", 64x64 tiles of every product through the tensor-core GEMM (mma.sync m8n8k4)";
     else
     {

@@ -611,6 +611,11 @@ int acro_b200_batched_gemm_t_supported(int m, int n, int k, int trans_a, int tra
 
 int acro_b200_batched_gemm_supported(int m, int n, int k) { return acro_b200_batched_gemm_t_supported(m, n, k, 0, 0); }
 
+int acro_b200_batched_gemm_by_pairs(int m, int n, int k, int trans_a, int trans_b)
+{
+    return batched_gemm_pairs_supported(m, n, k, trans_a ? 1 : 0, trans_b ? 1 : 0) ? 1 : 0;
+}
+
 int acro_b200_batched_gemm_t(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k, int trans_a, int trans_b, int op,
                              void *stream)
 {

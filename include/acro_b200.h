@@ -273,6 +273,9 @@ int acro_b200_batched_gemm(const double *A, const double *B, double *C, int64_t 
  * that stage whole matrices in shared memory; only the strides of their shared-memory reads change);
  * the same bit-identity up to 16 and tolerance above as the plain form. */
 int acro_b200_batched_gemm_t_supported(int m, int n, int k, int trans_a, int trans_b);
+/* 1 when products of this shape travel as PAIRS of elements by bulk copy (sizes 17 .. 32 whose stored rows have an odd
+ * length, operands on 16-byte boundaries) instead of through the zero-padded ring; for plan descriptions. */
+int acro_b200_batched_gemm_by_pairs(int m, int n, int k, int trans_a, int trans_b);
 int acro_b200_batched_gemm_t(const double *A, const double *B, double *C, int64_t batch, int m, int n, int k,
                              int trans_a, int trans_b, int op, void *stream);
 
