@@ -419,7 +419,7 @@ rank1_gemm_sym_kernel(const Rank1Args a)
 // One CTA of 16 warps per SM, as two groups of 8 warps.  A group works like a CTA of the old variant (its own
 // stream of 16-element tiles, W double buffer, image and bulk store, synchronised by a named barrier), so one
 // group's scatter and store overlap the other's tensor-core loop; warp w of either group uses the same
-// columns, so both groups read the one copy of BB that group 0 wrote.
+// columns, so both groups read the one copy of BB (each group writes half of its k-steps).
 constexpr int TM_GROUPS = 2, TM_GROUP_WARPS = 8, TM_GROUP_THREADS = TM_GROUP_WARPS * 32, TM_THREADS = TM_GROUPS * TM_GROUP_THREADS;
 constexpr int TM_NTW = 6, TM_MT = 2, TM_TE = TM_MT * 8;
 constexpr int TM_MAX_COLS = TM_GROUP_WARPS * TM_NTW * 8;          // 384 packed columns
@@ -521,9 +521,9 @@ rank1_gemm_sym_tmem_kernel(const Rank1Args a)
         }
     }
 
-    if (group == 0)
     {
-        // park this thread's fragment entries of BB: k-step ks, column tile nt at columns 12*ks + 2*nt (+1)
+        // park this thread's fragment entries of BB: k-step ks, column tile nt at columns 12*ks + 2*nt (+1).  Warp w of
+        // either group owns the same columns, so the two groups share the work: even k-steps by group 0, odd by group 1.
         int off1[NTW], off2[NTW];
 #pragma unroll
         for (int nt = 0; nt < NTW; ++nt)
@@ -532,7 +532,7 @@ rank1_gemm_sym_tmem_kernel(const Rank1Args a)
             c = c < n_cols ? c : n_cols - 1;        // padded columns compute a copy that is never stored
             unpack(c, off1[nt], off2[nt]);
         }
-        for (int ks = 0; ks < q_ext / 4; ++ks)
+        for (int ks = group; ks < q_ext / 4; ks += TM_GROUPS)
         {
             const double *b = sB + (4 * ks + t) * ldb;
             double v[NTW];
