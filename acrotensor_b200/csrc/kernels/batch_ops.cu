@@ -216,8 +216,18 @@ __global__ void flat_sum_gather_kernel(double *__restrict__ out, const double *_
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t d = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; d < domain; d += stride)
     {
+        // ascending position: the reference's order.  Four positions at a time: their indices, then their values, are
+        // fetched together (the kernel is bound by the latency of these dependent loads), the additions stay in order.
         double sum = 0.0;
-        for (int k = offsets[d]; k < offsets[d + 1]; ++k) sum = __dadd_rn(sum, in[inv_map[k]]);   // ascending position: the reference's order
+        int k = offsets[d];
+        const int end = offsets[d + 1];
+        for (; k + 4 <= end; k += 4)
+        {
+            const int i0 = inv_map[k], i1 = inv_map[k + 1], i2 = inv_map[k + 2], i3 = inv_map[k + 3];
+            const double v0 = in[i0], v1 = in[i1], v2 = in[i2], v3 = in[i3];
+            sum = __dadd_rn(__dadd_rn(__dadd_rn(__dadd_rn(sum, v0), v1), v2), v3);
+        }
+        for (; k < end; ++k) sum = __dadd_rn(sum, in[inv_map[k]]);
         out[d] = sum;
     }
 }

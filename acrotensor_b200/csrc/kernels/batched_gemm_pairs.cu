@@ -65,7 +65,9 @@ __device__ __forceinline__ void mbar_arrive_one(uint64_t *bar)
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
-template <bool TA, bool TB, bool ACC>
+// MC, NC, KC: the extents when known at compile time (the 27-wide cases, whose inner loop then unrolls and loses its
+// run-time predicates and index arithmetic), 0 = taken from the arguments.
+template <bool TA, bool TB, bool ACC, int MC = 0, int NC = 0, int KC = 0>
 __global__ void __launch_bounds__(kThreads, 2)
 batched_gemm_pairs_kernel(const PairArgs a)
 {
@@ -77,12 +79,12 @@ batched_gemm_pairs_kernel(const PairArgs a)
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int m = a.m, n = a.n, k = a.k;
+    const int m = MC ? MC : a.m, n = NC ? NC : a.n, k = KC ? KC : a.k;
     const int row_tiles = (m + 7) / 8;                 // per element
     const bool active = warp < 2 * row_tiles;          // this warp has a row tile of one element of the pair
     const int el = warp / row_tiles, m0 = (warp % row_tiles) * 8;
     const int k4 = (k + 3) & ~3;
-    const int lda = a.cols_a, ldb = a.cols_b;
+    const int lda = TA ? m : k, ldb = TB ? k : n;      // row lengths of the operands as stored
 
     if (tid == 0)
     {
@@ -143,6 +145,7 @@ batched_gemm_pairs_kernel(const PairArgs a)
             const double *sa = ring + stage * L.stage_doubles + el * (L.a_doubles / 2);
             const double *sb = ring + stage * L.stage_doubles + L.a_doubles + el * (L.b_doubles / 2);
             const int i = m0 + g;
+#pragma unroll (KC ? 8 : 1)
             for (int k0 = 0; k0 < k4; k0 += 4)
             {
                 const int kk = k0 + t;
@@ -222,8 +225,14 @@ template <bool ACC>
 int launch_pairs(const PairArgs &args, int trans_a, int trans_b, int grid, cudaStream_t stream, const char *where)
 {
     typedef void (*kernel_t)(const PairArgs);
-    const kernel_t kernel = trans_a ? (trans_b ? batched_gemm_pairs_kernel<true, true, ACC> : batched_gemm_pairs_kernel<true, false, ACC>)
-                                    : (trans_b ? batched_gemm_pairs_kernel<false, true, ACC> : batched_gemm_pairs_kernel<false, false, ACC>);
+    kernel_t kernel = trans_a ? (trans_b ? batched_gemm_pairs_kernel<true, true, ACC> : batched_gemm_pairs_kernel<true, false, ACC>)
+                              : (trans_b ? batched_gemm_pairs_kernel<false, true, ACC> : batched_gemm_pairs_kernel<false, false, ACC>);
+    // the sizes of a triquadratic hexahedron's element matrices, compiled in
+    if (args.m == 27 && args.n == 27)
+    {
+        if (ACC && trans_a && !trans_b && args.k == 32) kernel = batched_gemm_pairs_kernel<true, false, ACC, 27, 27, 32>;
+        if (!ACC && !trans_a && !trans_b && args.k == 27) kernel = batched_gemm_pairs_kernel<false, false, ACC, 27, 27, 27>;
+    }
     const PairLayout L = pair_layout(args, ACC);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
     if (status != cudaSuccess) return fail_cuda(status, where);

@@ -152,6 +152,9 @@ def launch_traffic(w, batch):
 
 def selected(workload):
     from acrotensor_b200.workloads import BY_KEY, WORKLOADS
+    only = os.environ.get("ACRO_BENCH_ONLY")          # debugging: a comma-separated subset of the suite
+    if workload == "suite" and only:
+        return [BY_KEY[k] for k in only.split(",")]
     return list(WORKLOADS) if workload == "suite" else [BY_KEY[workload]]
 
 
@@ -192,6 +195,17 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    t_start = time.perf_counter()
+    if os.environ.get("ACRO_BENCH_TRACE") == "1":
+        import faulthandler
+        import signal
+        faulthandler.register(signal.SIGUSR1, all_threads=True)      # kill -USR1 <pid>: where is the host?
+
+    def trace(what):
+        """Progress lines on stderr when ACRO_BENCH_TRACE=1 (to see where a multi-rank run spends its time)."""
+        if os.environ.get("ACRO_BENCH_TRACE") == "1":
+            print("[bench rank %d +%.1fs] %s" % (rank, time.perf_counter() - t_start, what), file=sys.stderr, flush=True)
 
     workloads = selected(args.workload)
     peer_group = None
@@ -263,7 +277,11 @@ def run_ours(args):
                 sess.t[name].SwitchToGPU()
         torch.cuda.synchronize()
 
+    sync_each = os.environ.get("ACRO_BENCH_SYNC_EACH") == "1"      # debugging: wait for every configuration and say so
+    step_no = [0]
+
     def device_step(events=None):
+        step_no[0] += 1
         for i, (w, sess) in enumerate(zip(workloads, sessions)):
             if events is not None:
                 events[i][0].record()
@@ -272,7 +290,13 @@ def run_ours(args):
                 allreduce_partial(outs_dev[i][w.names("out")[0]])
             if events is not None:
                 events[i][1].record()
+            if sync_each:
+                t_sync = time.perf_counter()
+                torch.cuda.synchronize()
+                trace("step %d %s done (%.1f ms), device status %d" % (step_no[0], w.key, (time.perf_counter() - t_sync) * 1e3,
+                                                                        ab.lib().acro_b200_device_status()))
 
+    trace("sessions ready")
     make_resident()
     barrier()      # all ranks enter the first step together (the fused all-reduce waits at most about a second)
     plans = [sess.plan_text() for sess in sessions]
@@ -281,6 +305,7 @@ def run_ours(args):
     for _ in range(args.warmup):
         device_step()
     barrier()
+    trace("warm-up done")
 
     def any_rank_gave_up():
         """True when a bounded device-side wait gave up on some rank since the last call (collective)."""
@@ -308,10 +333,13 @@ def run_ours(args):
         clocks = sampler.stop()
         ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in workloads]
               for _ in range(args.steps)]
+        barrier()      # stopping the sampler takes a different time on every rank; a peer of the fused all-reduce waits only about two seconds
         for k in range(args.steps):
             device_step(ev[k])
         barrier()
-        if not any_rank_gave_up():
+        gave_up = any_rank_gave_up()
+        trace("measurement %d done%s" % (attempt + 1, ", void: a bounded wait gave up on some rank" if gave_up else ""))
+        if not gave_up:
             break
     else:
         raise SystemExit("rank %d: a bounded device-side wait gave up in three measurements in a row" % rank)
@@ -326,6 +354,7 @@ def run_ours(args):
     across = contracted_parity(workloads, sessions, batches, world, rank, dev)
     if world > 1 and peer_group is not None:
         across["gram_rank_sum"] = gram_rank_sum_check(peer_group, world, rank, dev)
+    trace("parity checks done")
     if rank == 0:
         parity.update(across)
         if world == 1 and args.scale >= 1 and not args.no_cpu_baseline:
@@ -491,7 +520,14 @@ def run_ours(args):
         print(json.dumps(line))
     pool.shutdown()
     if world > 1:
+        # orderly exit: nobody unmaps or frees a mailbox while a peer may still be running a kernel that writes to it
+        barrier()
+        for sess in sessions:
+            sess.te.SetPeerGroup(None)
+        peer_group = None
+        barrier()
         dist.destroy_process_group()
+    trace("done")
 
 
 def contracted_parity(workloads, sessions, batches, world, rank, dev):
