@@ -264,3 +264,52 @@ def test_every_family_is_summed_over_two_ranks(tmp_path):
         elif "-=" in kernel:
             ref = 1.0 - ref
         assert oracle.parity_error(got, ref, mags + 1.0) <= TOL, name
+
+
+def _rank_late_peer(rank, world, port, out_dir):
+    import time
+    import torch
+    import torch.distributed as dist
+    from acrotensor_b200.runner import make_peer_group
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        group = make_peer_group()
+        a = torch.ones(4096, 9, dtype=torch.float64, device="cuda")
+        out = torch.zeros(9, dtype=torch.float64, device="cuda")
+        nbytes = lib().acro_b200_reduce_batch_scratch_bytes(9)
+        scratch = torch.empty(nbytes // 8 + 1, dtype=torch.float64, device="cuda")
+        p = lambda t: ctypes.c_void_p(t.data_ptr())
+        dist.barrier()
+        if rank == 1:
+            time.sleep(4.0)          # longer than the bounded wait: rank 0 gives up on its first calls, host-side delay only
+        record = []
+        for call in range(12):
+            t0 = time.perf_counter()
+            check(lib().acro_b200_reduce_batch_allreduce(p(a), None, p(out), 4096, 9, 0, p(scratch), nbytes, group._h, None))
+            status = lib().acro_b200_device_status()
+            record.append([float(status), float(out[0].item()), time.perf_counter() - t0])
+        np.save(os.path.join(out_dir, "late%d.npy" % rank), np.array(record))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_late_peer_times_out_then_the_exchange_recovers(tmp_path):
+    """A rank whose host is several seconds late (no GPU is held up on purpose: the delay is a sleep on the host) makes its
+    peer's bounded waits run out, which the peer sees as ETIMEOUT with the context intact; once the late rank has caught
+    up the ranks meet again and later calls give the right sum on both, without any repair step."""
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mp.spawn(_rank_late_peer, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    early, late = (np.load(os.path.join(str(tmp_path), "late%d.npy" % r)) for r in range(2))
+    print("early rank: status, value, seconds per call:", early.tolist())
+    assert int(early[0, 0]) == _lib.ETIMEOUT                      # the first wait of the early rank ran out ...
+    assert 0.2 < early[0, 2] < 6.0                                  # ... after a bounded time
+    assert np.all(late[:, 0] == _lib.OK)                          # the late rank finds every contribution already there
+    assert int(early[-1, 0]) == _lib.OK and early[-1, 1] == 8192.0 and late[-1, 1] == 8192.0
+    print("bounded wait took %.2f s; statuses of the early rank: %s" % (early[0, 2], early[:, 0].astype(int).tolist()))
+    assert np.count_nonzero(early[:, 0]) < 12 and np.all(np.diff((early[:, 0] != 0).astype(int)) <= 0)      # give-ups first, then none
