@@ -25,6 +25,7 @@ import os
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -68,17 +69,64 @@ def fp64_peak_gflops():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle sampling during the timed region (read-only queries)."""
+    """SM clock and throttle reasons during the timed region (read-only queries).  The timed region of a sharded run
+    lasts tens of milliseconds, so the samples come from NVML polled in a thread of this process every few
+    milliseconds; `nvidia-smi -lms` (a sample every 100 ms after a start-up of its own) is the fallback when the
+    NVML binding is missing."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
-    def __init__(self, gpu_index):
+    def __init__(self, gpu_index, period_s=0.002):
         self.gpu_index = gpu_index
+        self.period_s = period_s
         self.proc = None
         self.path = None
+        self.thread = None
+        self.samples = []          # (sm_mhz, reasons bit mask, watts)
+        self.sm_max = None
+        self.stop_flag = threading.Event()
+        self.first = 0
+
+    def mark(self):
+        """The timed region starts here: samples taken before it (an idle GPU) are left out."""
+        self.first = len(self.samples)
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.gpu_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+
+    def _poll(self, nv, handle):
+        while not self.stop_flag.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                try:
+                    watts = nv.nvmlDeviceGetPowerUsage(handle) / 1000.0
+                except Exception:
+                    watts = None
+                self.samples.append((float(mhz), int(mask), watts))
+            except Exception:
+                pass
+            self.stop_flag.wait(self.period_s)
 
     def start(self):
+        try:
+            nv, handle = self._nvml_handle()
+            self.sm_max = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -90,6 +138,20 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            self.samples = self.samples[self.first:] or self.samples
+            if not self.samples:
+                return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": ["no samples"], "source": "nvml"}
+            mask = 0
+            for _, m, _ in self.samples:
+                mask |= m
+            watts = [w for _, _, w in self.samples if w is not None]
+            return {"sm_mhz": float(np.median([c for c, _, _ in self.samples])), "sm_max_mhz": self.sm_max,
+                    "reasons": sorted(name for name, bit in self.REASON_BITS if mask & bit), "samples": len(self.samples),
+                    "sm_min_mhz": float(min(c for c, _, _ in self.samples)),
+                    "watts_max": float(max(watts)) if watts else None, "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -116,9 +178,9 @@ class ClockSampler:
                         reasons.add(name)
         os.unlink(self.path)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"], "source": "nvidia-smi"}
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)), "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvidia-smi"}
 
 
 def host_memory_available():
@@ -325,6 +387,7 @@ def run_ours(args):
         sampler.start()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
+        sampler.mark()
         t0.record()
         for k in range(args.steps):
             device_step()
