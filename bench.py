@@ -229,6 +229,21 @@ def local_batch(w, args, rank, world):
     return b1 - b0
 
 
+def config_of(args, world, workloads, batches):
+    """The `config` object of the record: both arms print the same one for the same command line (the
+    reference arm measures the whole job on the host, whatever the number of GPUs)."""
+    return {"workload": args.workload + (": cfg0..cfg4 back to back" if args.workload == "suite" else "")
+                        + (", benchmark sizes" if world == 1 else
+                           (", benchmark sizes cut into %d slabs (strong scaling)" % world if args.scaling == "strong"
+                            else ", a benchmark-size slab on each of %d ranks (weak scaling)" % world)),
+            "batches_per_gpu": {w.key: b for w, b in zip(workloads, batches)},
+            "l2": ("inputs_exceed_l2 (the smallest configuration streams %.0f MB per GPU per step, L2 holds 126 MB)"
+                   % (min(w.bytes(b) for w, b in zip(workloads, batches)) * 1e-6)) if args.scale >= 1 else "scaled-down run",
+            "parallelism": "batch slabs x%d, all-reduce only for the contracted batch index (%s)"
+                           % (world, "none needed" if world == 1 else
+                              ("fused into the reduction kernel over NVLink peer memory" if args.allreduce == "fused" else "NCCL"))}
+
+
 # ----------------------------------------------------------------------------- our arm
 
 def run_ours(args):
@@ -552,15 +567,7 @@ def run_ours(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
             "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f64",
             "data": "synthetic (seeded, shapes and distributions of the benchmark configurations)",
-            "config": {"workload": args.workload + (": cfg0..cfg4 back to back" if args.workload == "suite" else "")
-                                   + (", benchmark sizes" if world == 1 else
-                                      (", benchmark sizes cut into %d slabs (strong scaling)" % world if args.scaling == "strong"
-                                       else ", a benchmark-size slab on each of %d ranks (weak scaling)" % world)),
-                       "batches_per_gpu": {w.key: b for w, b in zip(workloads, batches)},
-                       "l2": "inputs_exceed_l2 (every configuration streams >= 1.6 GB per GPU)" if args.scale >= 1 else "scaled-down run",
-                       "parallelism": "batch slabs x%d, all-reduce only for the contracted batch index (%s)"
-                                      % (world, "none needed" if world == 1 else
-                                         ("fused into the reduction kernel over NVLink peer memory" if args.allreduce == "fused" else "NCCL"))},
+            "config": config_of(args, world, workloads, batches),
             "gflops": round(total_flops / ms_per_step * 1e-6, 1),
             "per_config": per_config,
             "per_config_note": "ms of each configuration from a second pass with an event on either side of it (median over the "
@@ -943,6 +950,7 @@ def run_reference(args):
     if not oracle.have("port"):
         oracle.build()
     workloads = selected(args.workload)
+    world = max(1, int(os.environ.get("WORLD_SIZE", str(args.gpus))))
     threads = host_threads() if oracle.have("ref") else 1
     # every pass is a bounded sample; the whole run stays within a few minutes
     per_pass = max(0.5, min(8.0, 150.0 / (args.steps + args.warmup)))
@@ -965,9 +973,10 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(float(np.median(secs)) * 1e3, 1), "higher_is_better": True, "scaling": args.scaling,
         "vs_baseline": None, "dtype": "f64", "data": "synthetic (seeded)",
-        "config": {"workload": args.workload + (": cfg0..cfg4 back to back" if args.workload == "suite" else ""),
-                   "note": "reference CPUInterpreted executor on the host cores; ms_per_step is the full-size suite extrapolated from the sample",
-                   "wall_s": round(wall, 1)},
+        "config": config_of(args, world, workloads, [local_batch(w, args, 0, world) for w in workloads]),
+        "reference_note": "reference CPUInterpreted executor on the host cores, the whole job (all slabs) on one host; "
+                          "ms_per_step is the full-size suite extrapolated from the sample",
+        "wall_s": round(wall, 1),
         "cpu_baseline": base,
         "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
