@@ -357,6 +357,29 @@ def run_ours(args):
     sync_each = os.environ.get("ACRO_BENCH_SYNC_EACH") == "1"      # debugging: wait for every configuration and say so
     step_no = [0]
 
+    # --streams per-config: the configurations are independent contractions, each engine launches on a stream of its
+    # own (TensorEngine::SetCudaStream) and the GPU runs them side by side; the instrumented pass stays on one stream
+    side = [torch.cuda.Stream(device=dev) for _ in workloads] if (args.streams == "per-config" and not use_nccl) else None
+
+    def use_side_streams(on):
+        if side is not None:
+            for sess, st in zip(sessions, side):
+                sess.te.SetCudaStream(st.cuda_stream if on else torch.cuda.current_stream().cuda_stream)
+
+    def fork():
+        if side is not None:
+            ev0 = torch.cuda.Event()
+            ev0.record()
+            for st in side:
+                st.wait_event(ev0)
+
+    def join():
+        if side is not None:
+            for st in side:
+                done = torch.cuda.Event()
+                done.record(st)
+                torch.cuda.current_stream().wait_event(done)
+
     def device_step(events=None):
         step_no[0] += 1
         for i, (w, sess) in enumerate(zip(workloads, sessions)):
@@ -402,19 +425,23 @@ def run_ours(args):
         sampler.start()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
+        use_side_streams(True)
         sampler.mark()
         t0.record()
+        fork()
         for k in range(args.steps):
             device_step()
+        join()
         t1.record()
         barrier()
-        clocks = sampler.stop()
+        use_side_streams(False)
         ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in workloads]
               for _ in range(args.steps)]
-        barrier()      # stopping the sampler takes a different time on every rank; a peer of the fused all-reduce waits only about two seconds
+        barrier()      # creating the events takes a different time on every rank; a peer of the fused all-reduce waits only about half a second
         for k in range(args.steps):
             device_step(ev[k])
         barrier()
+        clocks = sampler.stop()      # samples of both passes: the timed one and the instrumented one
         gave_up = any_rank_gave_up()
         trace("measurement %d done%s" % (attempt + 1, ", void: a bounded wait gave up on some rank" if gave_up else ""))
         if not gave_up:
@@ -998,6 +1025,8 @@ def main():
                     help="pinned host buffers for the end-to-end leg: all configurations at once, one at a time, or none")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="N > 1: how the contracted batch index of the README reduction is summed over ranks")
+    ap.add_argument("--streams", default="one", choices=["one", "per-config"],
+                    help="per-config: every configuration's engine launches on a stream of its own in the timed pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
