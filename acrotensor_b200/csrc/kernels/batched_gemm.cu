@@ -395,17 +395,47 @@ batched_gemm_padded_kernel(const PaddedArgs a)
     }
 }
 
-// Sum of `parts` partial tiles (ascending order: the same bits on every run with the same grid), applied to out.
-__global__ void __launch_bounds__(256)
+// Sum of `parts` partial tiles, applied to out.  A CTA takes 32 consecutive entries; its 16 rows of threads each sum
+// every sixteenth tile (eight loads in flight, each a warp-wide row of 256 contiguous bytes), then the first row adds
+// the 16 sums in ascending order: the order is fixed by `parts` alone, so the bits are the same on every run.  (One
+// thread per entry walking all the tiles took 50-100 us for 300-600 tiles, a chain of dependent L2 round trips.)
+constexpr int kCombineRows = 16;
+
+__global__ void __launch_bounds__(32 * kCombineRows)
 gram_combine_kernel(double *__restrict__ out, const double *__restrict__ partials, int parts, int entries, int op)
 {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= entries) return;
+    __shared__ double sums[kCombineRows][33];
+    const int i = blockIdx.x * 32 + threadIdx.x;
+    const int row = threadIdx.y;
     double acc = 0.0;
-    for (int p = 0; p < parts; ++p) acc = __dadd_rn(acc, __ldcg(partials + static_cast<int64_t>(p) * entries + i));
-    if (op == ACRO_B200_OP_ASSIGN) out[i] = acc;
-    else if (op == ACRO_B200_OP_ADD) out[i] = __dadd_rn(out[i], acc);
-    else out[i] = __dsub_rn(out[i], acc);
+    if (i < entries)
+    {
+        const double *src = partials + i;
+        int p = row;
+        for (; p + 7 * kCombineRows < parts; p += 8 * kCombineRows)
+        {
+            double v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + static_cast<int64_t>(p + u * kCombineRows) * entries);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc = __dadd_rn(acc, v[u]);
+        }
+        for (; p < parts; p += kCombineRows) acc = __dadd_rn(acc, __ldcg(src + static_cast<int64_t>(p) * entries));
+    }
+    sums[row][threadIdx.x] = acc;
+    __syncthreads();
+    if (row != 0 || i >= entries) return;
+    double total = sums[0][threadIdx.x];
+#pragma unroll
+    for (int r = 1; r < kCombineRows; ++r) total = __dadd_rn(total, sums[r][threadIdx.x]);
+    if (op == ACRO_B200_OP_ASSIGN) out[i] = total;
+    else if (op == ACRO_B200_OP_ADD) out[i] = __dadd_rn(out[i], total);
+    else out[i] = __dsub_rn(out[i], total);
+}
+
+void launch_gram_combine(double *out, const double *partials, int parts, int entries, int op, cudaStream_t stream)
+{
+    gram_combine_kernel<<<(entries + 31) / 32, dim3(32, kCombineRows), 0, stream>>>(out, partials, parts, entries, op);
 }
 
 template <int N>
@@ -726,7 +756,7 @@ int acro_b200_gram(const double *X, const double *Y, double *S, int64_t rows, in
         int tiles_written = 0;
         const int rc = gram_stream_launch(X, Y, scratch, rows, a, b, kGramMaxParts, &tiles_written, st);
         if (rc != ACRO_B200_OK) return rc;
-        gram_combine_kernel<<<(entries + 255) / 256, 256, 0, st>>>(S, scratch, tiles_written, entries, op);
+        launch_gram_combine(S, scratch, tiles_written, entries, op, st);
         return launch_status("acro_b200_gram (combine)");
     }
 
@@ -744,7 +774,7 @@ int acro_b200_gram(const double *X, const double *Y, double *S, int64_t rows, in
         rows -= pairs * 2 * slab;
         if (rows == 0)
         {
-            gram_combine_kernel<<<(entries + 255) / 256, 256, 0, st>>>(S, scratch, parts, entries, op);
+            launch_gram_combine(S, scratch, parts, entries, op, st);
             return launch_status("acro_b200_gram (combine)");
         }
     }
@@ -814,7 +844,7 @@ int acro_b200_gram(const double *X, const double *Y, double *S, int64_t rows, in
         if (launched != ACRO_B200_OK) return launched;
         ++parts;
     }
-    gram_combine_kernel<<<(entries + 255) / 256, 256, 0, st>>>(S, scratch, parts, entries, op);
+    launch_gram_combine(S, scratch, parts, entries, op, st);
     return launch_status("acro_b200_gram (combine)");
 }
 
