@@ -50,6 +50,19 @@ peer_allreduce_kernel(double *dst, const double *src, int64_t n, int op, PeerVie
 {
     __shared__ int gave_up;
     const int t = threadIdx.x;
+    if (n <= kPeerWordEntries)
+    {
+        // short results travel as self-marking words, the form of the reduction kernel's fused exchange: the ranks
+        // of one call may have planned different families, and the choice here depends on the result's size alone
+        const double total = exchange_words(pv, t, static_cast<int>(n), t < n ? src[t] : 0.0, wait_flag);
+        if (t < n)
+        {
+            if (op == ACRO_B200_OP_ASSIGN) dst[t] = total;
+            else if (op == ACRO_B200_OP_ADD) dst[t] += total;
+            else dst[t] -= total;
+        }
+        return;
+    }
     if (t == 0) gave_up = 0;
     __syncthreads();
     for (int64_t base = 0; base < n; base += kPeerSlot, ++pv.seq)

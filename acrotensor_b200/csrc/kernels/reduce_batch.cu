@@ -45,47 +45,6 @@ struct ReduceArgs
     int *wait_flag;     // raised when the bounded wait on the peers gives up
 };
 
-// Sum of this rank's total with the totals of all peer ranks, exchanged through the mailboxes
-// (see peer.cuh).  Called by the threads of the last CTA; `mine` is column t's total on this
-// rank (t < F).  Every rank adds the world totals in rank order, so all ranks obtain the same
-// bits.  The wait on the peers is bounded; when it runs out a flag is raised for the host and
-// the (then meaningless) result is still written, so nothing hangs.
-__device__ __forceinline__ double exchange_with_peers(const PeerView &pv, int t, int F, double mine, int *wait_flag)
-{
-    const int par = static_cast<int>(pv.seq & 1ull);
-    const size_t slot = (static_cast<size_t>(par) * pv.world + pv.rank) * kPeerSlot;
-    if (t < F)
-    {
-        for (int p = 0; p < pv.world; ++p) pv.data[p][slot + t] = mine;   // remote stores over the peer mapping
-        __threadfence_system();
-    }
-    __syncthreads();
-    if (t < pv.world)
-    {
-        // publish: this rank's data for call `seq` is complete in rank t's mailbox
-        volatile unsigned long long *remote = pv.flag[t] + static_cast<size_t>(par) * pv.world + pv.rank;
-        *remote = pv.seq;
-        // and wait until rank t's data has arrived in this rank's own mailbox
-        volatile unsigned long long *own = pv.flag[pv.rank] + static_cast<size_t>(par) * pv.world + t;
-        bool arrived = false;
-        for (unsigned int tries = 0; tries < (1u << 21); ++tries)   // about a second
-        {
-            if (*own >= pv.seq) { arrived = true; break; }
-            __nanosleep(64);
-        }
-        if (!arrived) atomicExch(wait_flag, 1);
-        __threadfence_system();
-    }
-    __syncthreads();
-    double total = 0.0;
-    if (t < F)
-    {
-        const volatile double *box = pv.data[pv.rank] + static_cast<size_t>(par) * pv.world * kPeerSlot;
-        for (int r = 0; r < pv.world; ++r) total += box[static_cast<size_t>(r) * kPeerSlot + t];
-    }
-    return total;
-}
-
 template <bool WEIGHTED, bool VECTOR, bool PEERS>
 __global__ void __launch_bounds__(kMaxThreads)
 reduce_batch_kernel(const ReduceArgs a, const PeerView pv)
@@ -191,7 +150,7 @@ reduce_batch_kernel(const ReduceArgs a, const PeerView pv)
     {
         for (int jj = 0; jj < J; ++jj) total += lanes[jj * F + t];
     }
-    if (PEERS) total = exchange_with_peers(pv, t, F, total, a.wait_flag);
+    if (PEERS) total = exchange_words(pv, t, F, total, a.wait_flag);
     if (t < F)
     {
         if (a.op == ACRO_B200_OP_ASSIGN) a.out[t] = total;
@@ -250,7 +209,7 @@ static int launch_reduce(const double *A, const double *w, double *out, int64_t 
     if (group != nullptr)
     {
         if (acro_b200_peer_group_is_connected(group) != 1) return fail_invalid("acro_b200_reduce_batch_allreduce: the peer group is not connected");
-        if (F > kPeerSlot) return fail_unsupported("acro_b200_reduce_batch_allreduce: row length exceeds the mailbox slot");
+        if (F > kPeerWordEntries) return fail_unsupported("acro_b200_reduce_batch_allreduce: row length exceeds the mailbox slot");
         args.wait_flag = wait_flag_device_ptr();
         if (args.wait_flag == nullptr) return fail_cuda(cudaErrorUnknown, "acro_b200_reduce_batch_allreduce (status flag)");
         pv = next_peer_view(group);
