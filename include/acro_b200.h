@@ -174,8 +174,10 @@ int acro_b200_reduce_batch_allreduce(const double *A, const double *w, double *o
                                      void *stream);
 /* The all-reduce on its own, for results any other kernel family left on each rank:
  * dst[i] (op)= sum over the ranks of src[i], i < n (src == dst allowed).  One small kernel; the entries
- * travel through the mailboxes in exchanges of at most 4096, summed in rank order (bit-identical on
- * every rank).  Every wait is bounded (about a second): an absent rank shows as ACRO_B200_ETIMEOUT in
+ * travel through the mailboxes in exchanges of at most 4096 (results of up to 256 entries in the form
+ * the fused exchange of acro_b200_reduce_batch_allreduce uses, so a rank may make either call for the
+ * same result), summed in rank order (bit-identical on every rank).  Every wait is bounded (about half
+ * a second): an absent rank shows as ACRO_B200_ETIMEOUT in
  * acro_b200_device_status() and the result is then invalid.  All ranks must make the same sequence of
  * calls, with the same n, on this group. */
 int acro_b200_peer_allreduce(double *dst, const double *src, int64_t n, int op, acro_b200_peer_group *group,
