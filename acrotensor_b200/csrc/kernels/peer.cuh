@@ -10,8 +10,9 @@
 // slots are enough: a rank cannot start call k+2 before every rank has published call k+1,
 // which each does only after it finished reading call k.
 //
-// The reduction kernel's fused exchange (row sums of at most 256 entries) uses the `word` area
-// instead and needs no fence: a double travels as two 8-byte words, each holding one half of its
+// Results of at most 256 entries (the reduction kernel's fused exchange, and the stand-alone
+// all-reduce for results of that size, so that the two are interchangeable) use the `word` area
+// instead and need no fence: a double travels as two 8-byte words, each holding one half of its
 // bits below the low 32 bits of the call's sequence number.  An 8-byte store arrives whole, so a
 // word whose upper half has reached the call's number holds that call's data; the receiver polls
 // the words themselves.  The fenced form costs two NVLink round trips per call (data, fence, flag,
@@ -69,7 +70,7 @@ __device__ __forceinline__ bool word_arrived(unsigned long long w, unsigned int 
 
 // Sum of this rank's total with the totals of all peer ranks, exchanged through the word area of the
 // mailboxes (above: every 8-byte word carries half a double and the call's number, so there is
-// no fence and no separate flag).  Called by all threads of the last CTA; `mine` is column t's total
+// no fence and no separate flag).  Called by all threads of one CTA; `mine` is column t's total
 // on this rank (t < F <= kPeerWordEntries).  Every (column, sender) pair is polled by a thread of its
 // own, then every rank adds the world totals in rank order, so all ranks obtain the same bits.  The
 // wait is bounded; when it runs out a flag is raised for the host and the (then meaningless) result
