@@ -129,11 +129,11 @@ batched_gemm_pairs_kernel(const PairArgs a)
             {
                 const int ns = static_cast<int>((it + AHEAD) % kStages);
                 const int64_t use = (it + AHEAD) / kStages;
-                if (use > 0 && !mbar_wait(&empty[ns], static_cast<uint32_t>((use - 1) & 1))) atomicExch(a.wait_flag, 1);
+                if (use > 0 && !mbar_wait_counted(&empty[ns], static_cast<uint32_t>((use - 1) & 1))) atomicExch(a.wait_flag, 1);
                 issue(nxt, ns);
             }
         }
-        if (!mbar_wait(&full[stage], static_cast<uint32_t>((it / kStages) & 1))) atomicExch(a.wait_flag, 1);
+        if (!mbar_wait_counted(&full[stage], static_cast<uint32_t>((it / kStages) & 1))) atomicExch(a.wait_flag, 1);
 
         if (!ACC)
         {

@@ -56,9 +56,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
     return done != 0;
 }
 
-// Bounded wait for the phase with the given parity.  Returns false when the limit ran out
-// (each try_wait already blocks for a hardware-defined interval, so the limit is seconds).
+// Bounded wait for the phase with the given parity.  Returns false when the limit ran out: about a second
+// (2e9 cycles of the SM's own counter, which is cheap to read; a try_wait blocks for a hardware-defined
+// interval of its own, so a count of tries alone bounds nothing that can be relied on), or max_tries,
+// whichever comes first.  The counter is read only after a first try has failed and then every sixteenth try.
+constexpr long long kMbarWaitLimitCycles = 2000000000ll;
+
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t max_tries = 1u << 22)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    for (uint32_t i = 0; i < max_tries; ++i)
+    {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 15u) == 15u && clock64() - start > kMbarWaitLimitCycles) return false;
+    }
+    return false;
+}
+
+// The same wait bounded by the number of tries alone.  Kept for the one kernel whose register allocation
+// (and with it 13 % of its speed) changed when the clock came into its waits.
+__device__ __forceinline__ bool mbar_wait_counted(uint64_t *bar, uint32_t parity, uint32_t max_tries = 1u << 22)
 {
     for (uint32_t i = 0; i < max_tries; ++i)
     {
