@@ -70,15 +70,16 @@ def fp64_peak_gflops():
 
 class ClockSampler:
     """SM clock and throttle reasons during the timed region (read-only queries).  The timed region of a sharded run
-    lasts tens of milliseconds, so the samples come from NVML polled in a thread of this process every few
-    milliseconds; `nvidia-smi -lms` (a sample every 100 ms after a start-up of its own) is the fallback when the
-    NVML binding is missing."""
+    lasts tens of milliseconds, so the samples come from NVML polled in a thread of this process every 10 ms
+    (not faster: every rank of a node polls, and the queries share the driver's locks with everything else);
+    `nvidia-smi -lms` (a sample every 100 ms after a start-up of its own) is the fallback when the NVML binding
+    is missing."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
     REASON_BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
-    def __init__(self, gpu_index, period_s=0.002):
+    def __init__(self, gpu_index, period_s=0.01):
         self.gpu_index = gpu_index
         self.period_s = period_s
         self.proc = None
