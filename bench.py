@@ -416,11 +416,11 @@ def run_ours(args):
         return bool(flag.item())
 
     # A rank whose host stalls for about a second while its launch queue is empty (a shared machine) makes
-    # its peers' bounded waits give up; such a measurement is void and is taken again, twice at most.
+    # its peers' bounded waits give up; such a measurement is void and is taken again, four times at most.
     # The step time is taken over launches that follow each other with nothing in between (an event between two
     # launches keeps the second from being brought onto the SMs while the first drains); the per-configuration
     # times come from a second pass of the same steps with an event on either side of every configuration.
-    for attempt in range(3):
+    for attempt in range(5):
         any_rank_gave_up()                       # clear what warm-up or an earlier attempt left
         sampler = ClockSampler(local_rank)
         sampler.start()
@@ -448,7 +448,7 @@ def run_ours(args):
         if not gave_up:
             break
     else:
-        raise SystemExit("rank %d: a bounded device-side wait gave up in three measurements in a row" % rank)
+        raise SystemExit("rank %d: a bounded device-side wait gave up in five measurements in a row" % rank)
     clocks["attempts"] = attempt + 1
     total_ms = t0.elapsed_time(t1)
     per_cfg_ms = [float(np.median([ev[k][i][0].elapsed_time(ev[k][i][1]) for k in range(args.steps)]))
