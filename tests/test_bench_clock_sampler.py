@@ -80,3 +80,29 @@ def test_failing_binding_falls_back_without_raising(monkeypatch):
     s.mark()
     rec = s.stop()
     assert rec["sm_mhz"] is None and rec["reasons"]
+
+
+def test_fallback_parses_nvidia_smi_lines(monkeypatch, tmp_path):
+    """Without the binding the sampler reads `nvidia-smi -lms` lines: a stand-in script prints two of them."""
+    broken = types.ModuleType("pynvml")
+
+    def init():
+        raise RuntimeError("driver not loaded")
+    broken.nvmlInit = init
+    monkeypatch.setitem(sys.modules, "pynvml", broken)
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/sh\n"
+                    "echo '0, 1950, 1965, 512.3, 0x0000000000000004, Not Active, Not Active, Not Active, Active'\n"
+                    "echo '0, 1935, 1965, 640.0, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active'\n"
+                    "sleep 5\n")
+    fake.chmod(0o755)
+    monkeypatch.setenv("PATH", str(tmp_path) + os.pathsep + os.environ.get("PATH", ""))
+    bench = load_bench()
+    s = bench.ClockSampler(0)
+    s.start()
+    s.mark()
+    time.sleep(0.3)
+    rec = s.stop()
+    assert rec["source"] == "nvidia-smi" and rec["samples"] == 2
+    assert rec["sm_mhz"] == 1942.5 and rec["sm_max_mhz"] == 1965.0
+    assert rec["reasons"] == ["sw_power_cap"]
